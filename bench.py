@@ -1,0 +1,427 @@
+#!/usr/bin/env python3
+"""Benchmark of the KV-cache attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input: append one new
+K/V row per sequence, then single-token attention over the whole cache (one layer).  The
+default workload is the decode microbenchmark (batch 64, 32 heads, head_dim 128, bf16,
+per-sequence cache length uniform in [512, 8192] from seed 0); the cache (9 GB) is far
+larger than L2, so no flush is needed between steps.  With N > 1 every rank (one per GPU,
+launched by torchrun) owns its own batch of 64 sequences and there is no collective in the
+step (weak scaling); time is the maximum over ranks.
+
+Rank 0 prints ONE JSON line.  ``value`` is decode tokens/s with inputs resident in HBM;
+``e2e`` is the same step through the public API with host buffers (pinned host -> device
+copies of q / new K / new V and the device -> host read of the output inside the timed
+region); ``roofline`` is the decode kernel's algorithmic HBM bytes over its CUDA-event time
+against the measured copy bandwidth; ``cpu_baseline`` is the CPU oracle (a port of the
+reference math, all host threads) on a bounded sample of the same workload.
+
+``--impl reference`` times that CPU port alone: the reference itself has no CPU or CUDA
+implementation of this path that can run here (its kernels are WGSL dispatched through
+wgpu / Vulkan, and this machine has no graphics stack).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (B, H, D, len_lo, len_hi, block_size, description)
+    "decode": dict(B=64, H=32, D=128, lo=512, hi=8192, block_size=0,
+                   desc="decode microbench: B=64 H=32 D=128 bf16, len~U[512,8192] seed 0, [B,H,T,D] cache"),
+    "paged": dict(B=64, H=32, D=128, lo=512, hi=8192, block_size=16,
+                  desc="paged decode: same shapes, 16-token blocks placed by a seeded permutation of 65536 blocks"),
+    "longctx": dict(B=4, H=64, D=128, lo=131072, hi=131072, block_size=0,
+                    desc="long-context decode: B=4 H=64 D=128 bf16, len 131072, batch-resident on one GPU"),
+}
+SLACK = 256  # rows of head-room above the longest sequence for the appended tokens
+
+
+def measured_hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.05):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(self.period)
+
+    def finish(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def make_lengths(w, seed):
+    rng = np.random.default_rng(seed)
+    if w["lo"] == w["hi"]:
+        return np.full(w["B"], w["lo"], dtype=np.int64)
+    return rng.integers(w["lo"], w["hi"] + 1, size=w["B"])
+
+
+def algorithmic_bytes(lens_after, H, D, es, B, block_size):
+    """Bytes the step must move: K and V rows of every attended token once, q, out, and the
+    append (read new K, V; write the rows).  Split-K partials are overhead, not counted."""
+    kv = int(np.sum(lens_after)) * H * D * 2 * es
+    qo = 2 * B * H * D * es
+    app = 4 * B * H * D * es
+    table = 4 * int(np.sum((lens_after + block_size - 1) // block_size)) if block_size else 0
+    return kv, kv + qo + app + table
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the oracle port on a bounded sample
+# ------------------------------------------------------------------------------------------
+
+def cpu_port_run(w, lens, steps, warmup, sample_seqs, log=None):
+    """Times append + decode of the CPU oracle (C, OpenMP, all host threads) on the first
+    `sample_seqs` sequences of the workload.  Returns (tokens_per_s, ms_per_step, threads)."""
+    from oracle import c_oracle, kv_oracle
+
+    Bs = min(sample_seqs, w["B"])
+    H, D = w["H"], w["D"]
+    sl = np.asarray(lens[:Bs], dtype=np.int32)
+    T_max = int(sl.max()) + SLACK
+    rng = np.random.default_rng(1234)
+    # bf16 bit patterns of N(0,1) samples; one shared block of rows keeps set-up time bounded
+    base_rows = kv_oracle.f32_to_bf16_bits(rng.standard_normal((4096, D)).astype(np.float32))
+    reps = (T_max + 4095) // 4096
+    one_head = np.tile(base_rows, (reps, 1))[:T_max]
+    k_cache = np.ascontiguousarray(np.broadcast_to(one_head[None, None], (Bs, H, T_max, D)))
+    v_cache = k_cache.copy()
+    q = kv_oracle.f32_to_bf16_bits(rng.standard_normal((Bs, H * D)).astype(np.float32))
+    nk = kv_oracle.f32_to_bf16_bits(rng.standard_normal((Bs, H * D)).astype(np.float32))
+    nv = kv_oracle.f32_to_bf16_bits(rng.standard_normal((Bs, H * D)).astype(np.float32))
+    strides = (H * T_max * D, D, T_max * D)
+    threads = c_oracle.num_threads()
+    pos = sl.copy()
+
+    def step():
+        c_oracle.append(nk, nv, k_cache, v_cache, pos, Bs, H, D, strides)
+        pos[:] += 1
+        return c_oracle.decode(q, k_cache, v_cache, pos, Bs, H, D, strides)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    ms = dt / steps * 1e3
+    return Bs / (dt / steps), ms, threads, Bs
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    lens = make_lengths(w, 0)
+    steps = max(1, args.steps)
+    warm = max(1, min(args.warmup, 3))
+    sample = 8 if w["B"] >= 8 else 1
+    # keep the whole run within a few minutes whatever K is
+    steps = min(steps, 20)
+    tps, ms, threads, Bs = cpu_port_run(w, lens, steps, warm, sample)
+    line = {
+        "impl": "reference",
+        "metric": "decode tokens/s",
+        "value": tps,
+        "unit": "tokens/s",
+        "n_gpus": args.gpus,
+        "steps": steps,
+        "warmup": warm,
+        "ms_per_step": ms,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16 storage, f64 accumulate",
+        "data": "synthetic",
+        "config": {"workload": w["desc"], "sample": f"first {Bs} sequences of the batch per step"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"append + decode of the first {Bs} of {w['B']} sequences, {steps} steps"},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU port of the reference math (oracle/kv_oracle.c); the reference's own WGSL path "
+                "needs wgpu/Vulkan: unavailable on this box",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+
+def run_b200(args, w, rank, world):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pkg = __graft_entry__.import_package()
+    gpu = pkg.gpu
+    ctx = gpu.context_create(local_rank)
+
+    B, H, D, bs = w["B"], w["H"], w["D"], w["block_size"]
+    E = H * D
+    dtype = torch.bfloat16
+    lens0 = make_lengths(w, rank)  # rank 0 draws the seed-0 lengths of the named config
+    T_max = int(lens0.max()) + SLACK
+    n_blocks = 0
+    if bs:
+        max_blocks = (T_max + bs - 1) // bs
+        n_blocks = max(65536, B * max_blocks)
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H,
+                                                       head_dim=D, dtype=dtype, layout="bhtd", ragged=True,
+                                                       block_size=bs, n_blocks=n_blocks))
+    if bs:
+        perm = np.random.default_rng(0).permutation(n_blocks)[: B * max_blocks].astype(np.int32)
+        cache.block_table = torch.from_numpy(perm.reshape(B, max_blocks)).to(device)
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    layer = cache.layers[0]
+    for buf in (layer.k_cache.buffer, layer.v_cache.buffer):
+        # N(0,1) in bf16, drawn in slabs to bound the fp32 temporary
+        flat = buf.view(-1)
+        slab = 1 << 28
+        for off in range(0, flat.numel(), slab):
+            n = min(slab, flat.numel() - off)
+            flat[off:off + n] = torch.randn(n, generator=gen, device=device, dtype=torch.float32).to(dtype)
+    q_dev = torch.randn((B, E), generator=gen, device=device, dtype=torch.float32).to(dtype)
+    nk_dev = torch.randn((B, E), generator=gen, device=device, dtype=torch.float32).to(dtype)
+    nv_dev = torch.randn((B, E), generator=gen, device=device, dtype=torch.float32).to(dtype)
+    out_dev = torch.empty((B, E), device=device, dtype=dtype)
+    wrap = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    q_b, nk_b, nv_b, out_b = wrap(q_dev), wrap(nk_dev), wrap(nv_dev), wrap(out_dev)
+
+    def reset_lengths():
+        gpu.kv_cache_set_lengths(cache, lens0)
+
+    def step_device():
+        gpu.batch_begin(ctx)
+        gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
+        gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
+        gpu.batch_commit(ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """K steps between two events on the launching stream; returns ms (max over ranks)."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    steps, warm = args.steps, max(3, args.warmup)
+    if steps + warm + 8 > SLACK // 2:
+        raise SystemExit(f"steps + warmup must stay below {SLACK // 2 - 8} (cache head-room)")
+
+    # ---- value: inputs resident in HBM -------------------------------------------------
+    reset_lengths()
+    for _ in range(warm):
+        step_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ms_total = timed(step_device, steps)
+    clocks = sampler.finish()
+    ms_step = ms_total / steps
+    tokens_per_s = world * B / (ms_step * 1e-3)
+
+    # ---- roofline: the decode call (split kernel + combine) alone, CUDA events ---------
+    reset_lengths()
+    cache.seq_lens.add_(1)  # the state the decode sees inside a step
+    cache.current_len = int(lens0.max()) + 1
+
+    def decode_only():
+        gpu.batch_begin(ctx)
+        gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
+        gpu.batch_commit(ctx)
+
+    for _ in range(3):
+        decode_only()
+    ms_dec = timed(decode_only, steps) / steps
+    kv_bytes, step_bytes = algorithmic_bytes(lens0 + 1, H, D, 2, B, bs)
+    dec_bytes = kv_bytes + 2 * B * E * 2 + (4 * int(np.sum((lens0 + bs) // bs)) if bs else 0)
+    peak, peak_kind = measured_hbm_peak()
+    achieved = dec_bytes / (ms_dec * 1e-3) / 1e9
+
+    # ---- e2e: host buffers through the public API --------------------------------------
+    reset_lengths()
+    q_host = q_dev.cpu().pin_memory()
+    nk_host = nk_dev.cpu().pin_memory()
+    nv_host = nv_dev.cpu().pin_memory()
+    out_host = torch.empty((B, E), dtype=dtype).pin_memory()
+
+    def step_e2e():
+        gpu.gpu_buffer_2d_write(ctx, q_host, q_b)
+        gpu.gpu_buffer_2d_write(ctx, nk_host, nk_b)
+        gpu.gpu_buffer_2d_write(ctx, nv_host, nv_b)
+        gpu.batch_begin(ctx)
+        gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
+        gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
+        gpu.batch_commit(ctx)
+        gpu.gpu_buffer_2d_read(ctx, out_b, out_host)  # blocks until the result is on the host
+
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, steps) / steps
+    e2e_tps = world * B / (ms_e2e * 1e-3)
+    h2d = 3 * B * E * 2
+    d2h = B * E * 2
+
+    # ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = 8 if B >= 8 else 1
+        tps, ms_cpu, threads, Bs = cpu_port_run(w, lens0, steps=6, warmup=1, sample_seqs=sample)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"append + decode of the first {Bs} of {B} sequences, 6 steps, {ms_cpu:.1f} ms/step"}
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "decode tokens/s",
+        "value": tokens_per_s,
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warm,
+        "ms_per_step": ms_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16 storage, fp32 arithmetic",
+        "data": "synthetic",
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
+                   "sum_len_rank0": int(np.sum(lens0)), "l2": "inputs (9 GB cache) far larger than L2, no flush",
+                   "parallelism": f"batch-sharded x{world}, no collective in the step"},
+        "e2e": {"value": e2e_tps, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": 3 * steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "decode_split_kernel + decode_combine_kernel (one b2kv_decode call)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "frac_of_8000_nominal": achieved / 8000.0, "peak_kind": peak_kind, "ms_per_launch": ms_dec,
+                     "algorithmic_bytes_per_launch": dec_bytes, "traffic": DRAM_TRAFFIC_PER_LAUNCH.get(args.workload)},
+        "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the split kernel from an ncu capture, scaled
+# to a full launch of the workload (see profiles/); None until captured.
+DRAM_TRAFFIC_PER_LAUNCH = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+    if world != args.gpus:
+        if args.gpus != 1 and world == 1:
+            raise SystemExit("launch with torchrun for --gpus > 1")
+    run_b200(args, w, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,150 @@
+/*
+ * b2kv - C ABI of the B200 (sm_100a) KV-cache attention kernels.
+ *
+ * These entry points take the place of the reference's WGSL dispatch
+ * (batch_add(ctx, kernel_source, params, buffers, workgroups...),
+ * simple-llm/src/gpu/gpu_ops.py:253-316) for the three operations of its KV-cache
+ * path.  Every argument is a plain device pointer, an integer or a stream handle;
+ * the library allocates nothing, keeps no pointer after a call returns, and
+ * launches asynchronously on the stream it is given (stream order takes the place
+ * of batch_begin / batch_commit, gpu_ops.py:226-250 and :343-360).
+ *
+ * Conventions
+ *   dtype        B2KV_DTYPE_F32 (the reference's only type) or B2KV_DTYPE_BF16
+ *                (storage type of q / k / v / caches / outputs; arithmetic is fp32).
+ *   cache layout element (b, t, h, d) lives at  b*stride_b + t*stride_t + h*stride_h + d
+ *                (strides in ELEMENTS, d contiguous).  The reference layout
+ *                [B*T_max, H*D] (gpu_kernels.py:2791-2796, :2858-2859) is
+ *                stride_b = T_max*H*D, stride_t = H*D, stride_h = D; the layout that
+ *                streams best on B200, [B, H, T_max, D], is stride_b = H*T_max*D,
+ *                stride_h = T_max*D, stride_t = D.
+ *   paged layout pools hold blocks of block_size tokens; token t of sequence b lives in
+ *                block  block_table[b*max_blocks + t/block_size]  at
+ *                blk*stride_blk + (t % block_size)*stride_t + h*stride_h + d.
+ *   lengths      seq_lens / seq_pos are int32 device arrays of B entries, or NULL to
+ *                use the single host integer (the reference's one current_len).
+ *   alignment    every pointer 16-byte aligned, D*sizeof(element) a multiple of 16,
+ *                every stride*sizeof(element) a multiple of 16.
+ *   stream       a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   return       0 on success, a negative B2KV_ERR_* code otherwise; nothing is
+ *                launched when an argument check fails.
+ *   dev_status   optional int32 device word (NULL to skip).  A kernel that detects a
+ *                block-table entry outside [0, n_blocks), a position outside the cache
+ *                or a wait that ran out stores a non-zero B2KV_DEV_* code there and
+ *                skips the access instead of faulting.  The caller zeroes and reads it.
+ */
+#ifndef B2KV_H
+#define B2KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2KV_DTYPE_F32 0
+#define B2KV_DTYPE_BF16 1
+
+#define B2KV_OK 0
+#define B2KV_ERR_BAD_ARG (-1)     /* NULL pointer, non-positive dimension, inconsistent sizes */
+#define B2KV_ERR_ALIGN (-2)       /* pointer or stride not 16-byte aligned                   */
+#define B2KV_ERR_UNSUPPORTED (-3) /* head_dim / dtype / block_size combination not compiled  */
+#define B2KV_ERR_WORKSPACE (-4)   /* workspace missing or smaller than *_workspace_bytes     */
+#define B2KV_ERR_CUDA (-5)        /* a CUDA runtime call failed; see b2kv_last_cuda_error    */
+
+#define B2KV_DEV_BAD_BLOCK 1    /* block-table entry outside the pool           */
+#define B2KV_DEV_BAD_POSITION 2 /* append position outside [0, T_max)           */
+#define B2KV_DEV_WAIT_TIMEOUT 3 /* a bounded wait on a copy barrier ran out     */
+
+/* Text for a return code.  Replaces the reference's exception messages at the C level. */
+const char* b2kv_strerror(int status);
+/* Text of the last CUDA runtime error seen by this library in the calling thread. */
+const char* b2kv_last_cuda_error(void);
+/* ABI version, bumped when a signature changes. */
+int b2kv_version(void);
+
+/*
+ * KV-cache append.  Replaces kv_cache_update's dispatch
+ * (simple-llm/src/gpu/gpu_kv_cache.py:161-184, kernel gpu_kernels.py:2725-2798):
+ * copies new_k / new_v [B, H*D] into the cache rows at position seq_pos[b]
+ * (or `pos` for every sequence when seq_pos is NULL).  Bit-exact copy with 16-byte
+ * vector stores.  The host owns the single current_len; with per-sequence positions and
+ * advance != 0 the kernel adds one to seq_pos[b] after the row is written (the device-side
+ * form of "cache.current_len += 1", gpu_kv_cache.py:186).
+ */
+int b2kv_append(const void* new_k, const void* new_v, void* k_cache, void* v_cache, int32_t* seq_pos, int pos,
+                int advance, int B, int H, int D, int T_max, int64_t stride_b, int64_t stride_t, int64_t stride_h,
+                int dtype, int32_t* dev_status, void* stream);
+
+/* Paged variant of b2kv_append (block table, no counterpart in the reference: its cache is
+ * one contiguous buffer per layer, gpu_kv_cache.py:66-78). */
+int b2kv_append_paged(const void* new_k, const void* new_v, void* k_pool, void* v_pool, int32_t* seq_pos, int pos,
+                      int advance, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
+                      int H, int D, int64_t stride_blk, int64_t stride_t, int64_t stride_h, int dtype,
+                      int32_t* dev_status, void* stream);
+
+/*
+ * Cache gather: writes the logical view out[B, T_out, H, D] (contiguous) of the first
+ * seq_lens[b] (or `len`) rows of every sequence, zero beyond.  The reference reads caches
+ * back with gpu_buffer_2d_read (simple-llm/src/gpu/gpu_buffer.py:198-208), which only
+ * works for its own layout; this is the layout-independent equivalent used for bit-exact
+ * append / gather checks.
+ */
+int b2kv_gather(const void* cache, void* out, const int32_t* seq_lens, int len, int B, int H, int D, int T_out,
+                int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype, void* stream);
+int b2kv_gather_paged(const void* pool, void* out, const int32_t* seq_lens, int len, const int32_t* block_table,
+                      int max_blocks, int block_size, int n_blocks, int B, int H, int D, int T_out, int64_t stride_blk,
+                      int64_t stride_t, int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
+
+/*
+ * Single-token decode attention over the cache.  Replaces attention_with_kv_cache's
+ * dispatch (simple-llm/src/gpu/gpu_kv_cache.py:266-289, kernel gpu_kernels.py:2801-2938):
+ * out[b, h, :] = softmax(q[b, h, :] . K[b, 0:n_b, h, :]^T / sqrt(D)) . V[b, 0:n_b, h, :]
+ * with n_b = (seq_lens ? seq_lens[b] : len) + len_bias, clamped to [0, T_upper].
+ * q, out are [B, H*D].  Sequences with n_b == 0 produce zeros.  The reference's limit of
+ * 256 cached tokens (gpu_kv_cache.py:250-257) does not exist here: the cache is
+ * processed split-K (flash decoding) and the partial results are merged by a second
+ * small kernel.  T_upper is a host-side upper bound of every n_b (at most T_max); it
+ * sizes the workspace and the split.  len_bias lets a caller attend over "length after
+ * this step's append" without a separate increment of the device lengths.
+ * `workspace` is scratch of at least b2kv_decode_workspace_bytes(...) bytes; it needs no
+ * initialisation and carries nothing between calls.
+ */
+size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper);
+int b2kv_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens, int len,
+                int len_bias, int B, int H, int D, int T_upper, int64_t stride_b, int64_t stride_t, int64_t stride_h,
+                int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream);
+int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, void* out, const int32_t* seq_lens,
+                      int len, int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks,
+                      int B, int H, int D, int T_upper, int64_t stride_blk, int64_t stride_t, int64_t stride_h,
+                      int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream);
+
+/*
+ * Causal flash-attention prefill.  Replaces flash_attention's dispatch
+ * (simple-llm/src/gpu/gpu_pass_forward.py:557-588, kernel gpu_kernels.py:499-770).
+ * Q, K, V, O are [B*N, H*D]; L and M (float, [B*N*H], index b*N*H + row*H + h, either may
+ * be NULL) receive the softmax row sums and row maxima of the scaled scores as the
+ * reference kernel writes them (gpu_kernels.py:762-768).  Key j is visible to query i when
+ * j <= i.  When k_cache / v_cache are non-NULL the kernel also writes K / V rows 0..N-1 of
+ * every sequence into the caches (same dtype, layout given by the cache strides), which
+ * the reference can only do one token at a time through kv_cache_update.
+ * bf16 with D == 128 runs on the tcgen05 tensor cores; other shapes run on a SIMT kernel.
+ */
+int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache,
+                 void* v_cache, int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B, int N, int H,
+                 int D, int dtype, void* stream);
+
+/*
+ * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
+ * "decode_chunk", "decode_grid_per_sm", "prefill_force_simt"); returns B2KV_ERR_BAD_ARG
+ * for an unknown name.  Defaults are chosen per shape when a knob is 0.  No counterpart in
+ * the reference beyond the tile-size fields of GPUConfig (gpu_types.py:69-121).
+ */
+int b2kv_tune(const char* name, int value);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B2KV_H */

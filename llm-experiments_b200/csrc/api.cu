@@ -1,0 +1,81 @@
+// Library-level entry points: status text, CUDA error record, tuning knobs.
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "b2kv_common.cuh"
+
+namespace b2kv {
+
+static thread_local char g_last_error[256] = "no error";
+
+int note_cuda_error(cudaError_t e, const char* where) {
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", cudaGetErrorName(e), cudaGetErrorString(e), where);
+    cudaGetLastError();  // clear the sticky-free error so that the next call starts clean
+    return B2KV_ERR_CUDA;
+}
+
+struct Knob {
+    const char* name;
+    int value;
+};
+
+static Knob g_knobs[] = {
+    {"decode_variant", 0},      // which compiled (tile, stages, warps) variant of the split kernel
+    {"decode_chunk", 0},        // tokens per split; 0 = chosen from the shape
+    {"decode_grid_per_sm", 0},  // resident CTAs per SM to launch; 0 = occupancy
+    {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
+    {"prefill_variant", 0},
+};
+
+int tune_get(const char* name) {
+    for (auto& k : g_knobs)
+        if (strcmp(k.name, name) == 0) return k.value;
+    return 0;
+}
+
+int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace b2kv
+
+extern "C" {
+
+const char* b2kv_strerror(int status) {
+    switch (status) {
+        case B2KV_OK: return "ok";
+        case B2KV_ERR_BAD_ARG: return "bad argument (null pointer, non-positive dimension or inconsistent sizes)";
+        case B2KV_ERR_ALIGN: return "pointer or stride is not 16-byte aligned";
+        case B2KV_ERR_UNSUPPORTED: return "unsupported head_dim / dtype / block_size combination";
+        case B2KV_ERR_WORKSPACE: return "workspace missing or too small";
+        case B2KV_ERR_CUDA: return "CUDA runtime error (see b2kv_last_cuda_error)";
+        default: return "unknown status";
+    }
+}
+
+const char* b2kv_last_cuda_error(void) { return b2kv::g_last_error; }
+
+int b2kv_version(void) { return 1; }
+
+int b2kv_tune(const char* name, int value) {
+    if (name == nullptr) return B2KV_ERR_BAD_ARG;
+    for (auto& k : b2kv::g_knobs) {
+        if (strcmp(k.name, name) == 0) {
+            k.value = value;
+            return B2KV_OK;
+        }
+    }
+    return B2KV_ERR_BAD_ARG;
+}
+
+}  // extern "C"

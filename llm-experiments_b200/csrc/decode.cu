@@ -1,0 +1,593 @@
+// Single-token decode attention over the KV cache: split-K flash decoding for sm_100a.
+//
+// The reference kernel (simple-llm/src/gpu/gpu_kernels.py:2801-2938) gives one workgroup
+// to each (sequence, head), keeps the whole score vector in workgroup memory (hence its
+// 256-token limit) and reads K rows uncoalesced.  Here the cache is cut into work items of
+// `chunk` tokens of one (sequence, head); a persistent grid of CTAs walks the items
+// round-robin.  Inside a CTA one producer warp streams K/V tiles from HBM into a ring of
+// shared-memory stages with bulk copies (TMA, untiled) that complete on mbarriers, and the
+// consumer warps fold each tile into an online softmax held in registers.  The producer
+// runs ahead across item boundaries, so the copy queue never drains between items.  Each
+// item leaves one partial (m, l, acc[D]) in the workspace; a small second kernel merges
+// the partials of every (sequence, head).
+//
+// Arithmetic: storage type fp32 or bf16, all math in fp32; scores are kept in the log2
+// domain (q is pre-multiplied by log2(e)/sqrt(D)) so that exp is a single ex2.
+//
+// HBM traffic per launch is the K and V rows of the attended tokens, once:
+// sum_b n_b * H * D * 2 * sizeof(element), plus q, out and the partials.
+#include <math.h>
+
+#include "b2kv_common.cuh"
+
+namespace b2kv {
+
+constexpr int kFlagFirst = 1;  // first tile of an item: reset the running softmax, take q
+constexpr int kFlagLast = 2;   // last tile of an item: merge the warps and store the partial
+constexpr int kFlagDone = 4;   // no more work for this CTA
+
+struct StageMeta {
+    int slot;   // partial-result slot of the item this tile belongs to
+    int ntok;   // valid rows in the tile
+    int flags;
+    int pad;
+};
+
+struct DecodeParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    float* ws_acc;  // [slots, D]
+    float* ws_ml;   // [slots, 2]
+    const int32_t* seq_lens;
+    const int32_t* block_table;
+    int32_t* dev_status;
+    int len_scalar, len_bias;
+    int B, H, T_upper;
+    int chunk, c_max;  // tokens per item, items per (b, h) at most
+    int max_blocks, block_size, n_blocks;
+    int run_len;  // tokens that one bulk copy may cover (contiguous in memory)
+    int64_t stride_b, stride_t, stride_h;
+    float q_prescale;
+};
+
+__device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
+    int n = (p.seq_lens ? p.seq_lens[b] : p.len_scalar) + p.len_bias;
+    return min(max(n, 0), p.T_upper);
+}
+
+template <typename T, int D, int TILE_T, int STAGES, int NCW>
+struct DecodeCfg {
+    static constexpr int kRowBytes = D * static_cast<int>(sizeof(T));
+    static constexpr int kTileBytes = TILE_T * kRowBytes;
+    static constexpr int kStageBytes = 2 * kTileBytes + kRowBytes;  // K tile, V tile, q row
+    static constexpr int kChunksPerRow = kRowBytes / 16;
+    static constexpr int kLanesPerRow = kChunksPerRow < 32 ? kChunksPerRow : 32;
+    static constexpr int kChunksPerLane = kChunksPerRow / kLanesPerRow;
+    static constexpr int kRowsPerPass = 32 / kLanesPerRow;
+    static constexpr int kRowsPerWarp = TILE_T / NCW;
+    static constexpr int kPasses = kRowsPerWarp / kRowsPerPass;
+    static constexpr int kBatch = kPasses < 8 ? kPasses : 8;
+    static constexpr int kEpc = Elt<T>::kPerChunk;
+    static constexpr int kAcc = kChunksPerLane * kEpc;
+    static constexpr int kMergeFloats = NCW * (D + 2);
+    static constexpr int kThreads = (NCW + 1) * 32;
+    static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + 2 * STAGES * sizeof(uint64_t) +
+                                         STAGES * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 128;
+    static_assert(kRowBytes % 16 == 0, "rows must be whole 16-byte chunks");
+    static_assert(kChunksPerRow >= 2, "a row must span at least two lanes");
+    static_assert(TILE_T % NCW == 0 && kRowsPerWarp % kRowsPerPass == 0 && kPasses % kBatch == 0, "tile split");
+};
+
+// --------------------------------------------------------------------------------------
+// producer warp
+// --------------------------------------------------------------------------------------
+
+template <typename Cfg, typename T, int D, int TILE_T, int STAGES>
+__device__ __forceinline__ void decode_producer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
+                                                uint64_t* empty, StageMeta* meta, int lane) {
+    const char* kbase = static_cast<const char*>(p.k);
+    const char* vbase = static_cast<const char*>(p.v);
+    const char* qbase = static_cast<const char*>(p.q);
+    int stage = 0;
+    uint32_t phase = 0;
+    long long fills = 0;  // stages filled so far (for the drain after a failed wait)
+    bool ok = true;
+
+    int b = 0;
+    long long base = 0;  // items that precede sequence b
+    int len_b = seq_len_of(p, 0);
+    int nch_b = (len_b + p.chunk - 1) / p.chunk;
+
+    for (long long w = blockIdx.x; ok; w += gridDim.x) {
+        while (b < p.B && w >= base + static_cast<long long>(p.H) * nch_b) {
+            base += static_cast<long long>(p.H) * nch_b;
+            ++b;
+            if (b < p.B) {
+                len_b = seq_len_of(p, b);
+                nch_b = (len_b + p.chunk - 1) / p.chunk;
+            }
+        }
+        if (b >= p.B) break;
+        const int local = static_cast<int>(w - base);
+        const int c = local / p.H;
+        const int h = local - c * p.H;
+        const int t_begin = c * p.chunk;
+        const int t_end = min(len_b, t_begin + p.chunk);
+        const int slot = (b * p.H + h) * p.c_max + c;
+
+        for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
+            const int ntok = min(TILE_T, t_end - t0);
+            if (!mbar_wait(&empty[stage], phase ^ 1u)) {
+                ok = false;
+                break;
+            }
+            uint8_t* sbase = stages + static_cast<size_t>(stage) * Cfg::kStageBytes;
+            const bool first = (t0 == t_begin);
+            if (lane == 0) {
+                StageMeta mt;
+                mt.slot = slot;
+                mt.ntok = ntok;
+                mt.flags = (first ? kFlagFirst : 0) | (t0 + TILE_T >= t_end ? kFlagLast : 0);
+                mt.pad = 0;
+                meta[stage] = mt;
+                const uint32_t bytes =
+                    2u * static_cast<uint32_t>(ntok) * Cfg::kRowBytes + (first ? Cfg::kRowBytes : 0);
+                mbar_arrive_expect_tx(&full[stage], bytes);
+            }
+            __syncwarp();
+            if (first && lane == 31) {
+                bulk_g2s(sbase + 2 * Cfg::kTileBytes,
+                         qbase + (static_cast<size_t>(b) * p.H + h) * Cfg::kRowBytes, Cfg::kRowBytes, &full[stage]);
+            }
+            const int nruns = (ntok + p.run_len - 1) / p.run_len;
+            for (int r = lane; r < nruns; r += 32) {
+                const int tok = t0 + r * p.run_len;
+                const int cnt = min(p.run_len, t0 + ntok - tok);
+                int64_t off;
+                if (p.block_table == nullptr) {
+                    off = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(tok) * p.stride_t;
+                } else {
+                    int blk = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+                    if (blk < 0 || blk >= p.n_blocks) {
+                        report_status(p.dev_status, B2KV_DEV_BAD_BLOCK);
+                        blk = 0;  // stay inside the pool; the status word tells the caller
+                    }
+                    off = static_cast<int64_t>(blk) * p.stride_b +
+                          static_cast<int64_t>(tok % p.block_size) * p.stride_t;
+                }
+                off = (off + static_cast<int64_t>(h) * p.stride_h) * static_cast<int64_t>(sizeof(T));
+                const uint32_t bytes = static_cast<uint32_t>(cnt) * Cfg::kRowBytes;
+                const int dst = (tok - t0) * Cfg::kRowBytes;
+                bulk_g2s(sbase + dst, kbase + off, bytes, &full[stage]);
+                bulk_g2s(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage]);
+            }
+            ++fills;
+            if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1u;
+            }
+        }
+    }
+
+    if (ok && mbar_wait(&empty[stage], phase ^ 1u)) {
+        if (lane == 0) {
+            StageMeta mt;
+            mt.slot = 0;
+            mt.ntok = 0;
+            mt.flags = kFlagDone;
+            mt.pad = 0;
+            meta[stage] = mt;
+            mbar_arrive(&full[stage]);
+        }
+        return;
+    }
+    // A wait ran out: tell the host, then make sure no copy of ours is still in flight
+    // towards this CTA's shared memory before the warp leaves.
+    report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+    for (long long f = max(0ll, fills - STAGES); f < fills; ++f)
+        (void)mbar_wait(&full[f % STAGES], static_cast<uint32_t>((f / STAGES) & 1));
+}
+
+// --------------------------------------------------------------------------------------
+// consumer warps
+// --------------------------------------------------------------------------------------
+
+template <typename Cfg, typename T, int D, int TILE_T, int STAGES, int NCW>
+__device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
+                                                uint64_t* empty, const StageMeta* meta, float* merge, int warp,
+                                                int lane) {
+    constexpr int LPR = Cfg::kLanesPerRow;
+    constexpr int CPL = Cfg::kChunksPerLane;
+    constexpr int EPC = Cfg::kEpc;
+    constexpr int NACC = Cfg::kAcc;
+    constexpr int RPP = Cfg::kRowsPerPass;
+    constexpr int RPW = Cfg::kRowsPerWarp;
+    constexpr int BATCH = Cfg::kBatch;
+    const int g = lane / LPR;  // which of the RPP rows of a pass this lane works on
+    const int j = lane % LPR;  // which 16-byte chunk(s) of the row
+
+    float acc[NACC], qf[NACC];
+    float m = -INFINITY, l = 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+        acc[i] = 0.f;
+        qf[i] = 0.f;
+    }
+
+    int stage = 0;
+    uint32_t phase = 0;
+    int parity = 0;  // which merge buffer the next finished item uses
+
+    while (true) {
+        if (!mbar_wait(&full[stage], phase)) {
+            report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+            return;
+        }
+        const StageMeta mt = meta[stage];
+        if (mt.flags & kFlagDone) return;
+        const uint8_t* Ks = stages + static_cast<size_t>(stage) * Cfg::kStageBytes;
+        const uint8_t* Vs = Ks + Cfg::kTileBytes;
+
+        if (mt.flags & kFlagFirst) {
+            m = -INFINITY;
+            l = 0.f;
+#pragma unroll
+            for (int c = 0; c < CPL; ++c) {
+                const uint4 qc = *reinterpret_cast<const uint4*>(Ks + 2 * Cfg::kTileBytes + (c * LPR + j) * 16);
+                Elt<T>::widen(qc, &qf[c * EPC]);
+            }
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) {
+                qf[i] *= p.q_prescale;
+                acc[i] = 0.f;
+            }
+        }
+
+        const int row0 = warp * RPW;
+        if (row0 < mt.ntok) {
+#pragma unroll 1
+            for (int ib = 0; ib < Cfg::kPasses; ib += BATCH) {
+                float s[BATCH];
+#pragma unroll
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = row0 + (ib + i) * RPP + g;
+                    float part = 0.f;
+                    if (r < mt.ntok) {
+#pragma unroll
+                        for (int c = 0; c < CPL; ++c) {
+                            const uint4 kc =
+                                *reinterpret_cast<const uint4*>(Ks + r * Cfg::kRowBytes + (c * LPR + j) * 16);
+                            float kf[EPC];
+                            Elt<T>::widen(kc, kf);
+#pragma unroll
+                            for (int e = 0; e < EPC; ++e) part = fmaf(qf[c * EPC + e], kf[e], part);
+                        }
+                    }
+                    s[i] = part;
+                }
+#pragma unroll
+                for (int off = LPR / 2; off >= 1; off >>= 1) {
+#pragma unroll
+                    for (int i = 0; i < BATCH; ++i) s[i] += __shfl_xor_sync(0xffffffffu, s[i], off);
+                }
+                float m_new = m;
+#pragma unroll
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = row0 + (ib + i) * RPP + g;
+                    if (r >= mt.ntok) s[i] = -INFINITY;
+                    m_new = fmaxf(m_new, s[i]);
+                }
+                // every row of this lane group masked so far: keep exp2 arguments finite
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float corr = exp2f(m - m_use);
+                l *= corr;
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+#pragma unroll
+                for (int i = 0; i < BATCH; ++i) {
+                    const int r = row0 + (ib + i) * RPP + g;
+                    if (r < mt.ntok) {
+                        const float pr = exp2f(s[i] - m_use);
+                        l += pr;
+#pragma unroll
+                        for (int c = 0; c < CPL; ++c) {
+                            const uint4 vc =
+                                *reinterpret_cast<const uint4*>(Vs + r * Cfg::kRowBytes + (c * LPR + j) * 16);
+                            float vf[EPC];
+                            Elt<T>::widen(vc, vf);
+#pragma unroll
+                            for (int e = 0; e < EPC; ++e) acc[c * EPC + e] = fmaf(pr, vf[e], acc[c * EPC + e]);
+                        }
+                    }
+                }
+                m = m_new;
+            }
+        }
+
+        // all reads of this stage are done: hand it back to the producer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);
+        if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+        }
+
+        if (mt.flags & kFlagLast) {
+            // merge the RPP lane groups of this warp
+#pragma unroll
+            for (int off = LPR; off < 32; off <<= 1) {
+                const float m_o = __shfl_xor_sync(0xffffffffu, m, off);
+                const float l_o = __shfl_xor_sync(0xffffffffu, l, off);
+                const float m_n = fmaxf(m, m_o);
+                const float m_u = (m_n == -INFINITY) ? 0.f : m_n;
+                const float a = exp2f(m - m_u), bsc = exp2f(m_o - m_u);
+                l = l * a + l_o * bsc;
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) {
+                    const float o = __shfl_xor_sync(0xffffffffu, acc[i], off);
+                    acc[i] = acc[i] * a + o * bsc;
+                }
+                m = m_n;
+            }
+            float* mb = merge + parity * Cfg::kMergeFloats + warp * (D + 2);
+            if (g == 0) {
+#pragma unroll
+                for (int c = 0; c < CPL; ++c)
+#pragma unroll
+                    for (int e = 0; e < EPC; ++e) mb[(c * LPR + j) * EPC + e] = acc[c * EPC + e];
+                if (j == 0) {
+                    mb[D] = m;
+                    mb[D + 1] = l;
+                }
+            }
+            named_barrier_sync<NCW * 32>(1);
+            // all consumer threads: one output column each
+            const float* mr = merge + parity * Cfg::kMergeFloats;
+            float m_all = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NCW; ++w) m_all = fmaxf(m_all, mr[w * (D + 2) + D]);
+            const float m_u = (m_all == -INFINITY) ? 0.f : m_all;
+            float wgt[NCW];
+            float l_all = 0.f;
+#pragma unroll
+            for (int w = 0; w < NCW; ++w) {
+                wgt[w] = exp2f(mr[w * (D + 2) + D] - m_u);
+                l_all += wgt[w] * mr[w * (D + 2) + D + 1];
+            }
+            const int tid = warp * 32 + lane;
+            for (int d = tid; d < D; d += NCW * 32) {
+                float o = 0.f;
+#pragma unroll
+                for (int w = 0; w < NCW; ++w) o += wgt[w] * mr[w * (D + 2) + d];
+                p.ws_acc[static_cast<size_t>(mt.slot) * D + d] = o;
+            }
+            if (tid == 0) {
+                p.ws_ml[static_cast<size_t>(mt.slot) * 2] = m_all;
+                p.ws_ml[static_cast<size_t>(mt.slot) * 2 + 1] = l_all;
+            }
+            parity ^= 1;
+        }
+    }
+}
+
+template <typename T, int D, int TILE_T, int STAGES, int NCW>
+__global__ void __launch_bounds__((NCW + 1) * 32) decode_split_kernel(const DecodeParams p) {
+    using Cfg = DecodeCfg<T, D, TILE_T, STAGES, NCW>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * Cfg::kStageBytes);
+    uint64_t* empty = full + STAGES;
+    StageMeta* meta = reinterpret_cast<StageMeta*>(empty + STAGES);
+    float* merge = reinterpret_cast<float*>(meta + STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NCW);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (warp == NCW) {
+        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, stages, full, empty, meta, lane);
+    } else {
+        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, meta, merge, warp, lane);
+    }
+}
+
+// One CTA per (sequence, head), one thread per output column.
+template <typename T, int D>
+__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeParams p, T* __restrict__ out) {
+    const int bh = blockIdx.x;
+    const int b = bh / p.H;
+    const int d = threadIdx.x;
+    const int n = seq_len_of(p, b);
+    const int nch = (n + p.chunk - 1) / p.chunk;
+    const size_t slot0 = static_cast<size_t>(bh) * p.c_max;
+    float m_all = -INFINITY;
+    for (int c = 0; c < nch; ++c) m_all = fmaxf(m_all, p.ws_ml[(slot0 + c) * 2]);
+    float l_all = 0.f, o = 0.f;
+    for (int c = 0; c < nch; ++c) {
+        const float wgt = exp2f(p.ws_ml[(slot0 + c) * 2] - m_all);
+        l_all += wgt * p.ws_ml[(slot0 + c) * 2 + 1];
+        o += wgt * p.ws_acc[(slot0 + c) * D + d];
+    }
+    out[static_cast<size_t>(bh) * D + d] = Elt<T>::from_float(nch > 0 ? o / l_all : 0.f);
+}
+
+// --------------------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------------------
+
+static int pick_chunk(int B, int H, int T_upper, int tile, int grid_ctas) {
+    int forced = tune_get("decode_chunk");
+    if (forced > 0) return ((forced + tile - 1) / tile) * tile;
+    // enough items to give every resident CTA several, but items long enough to amortise
+    // the per-item merge: between one tile and eight tiles.
+    long long tiles_total = static_cast<long long>(B) * H * ((T_upper + tile - 1) / tile);
+    long long per = tiles_total / (4ll * grid_ctas);
+    if (per < 1) per = 1;
+    if (per > 8) per = 8;
+    return static_cast<int>(per) * tile;
+}
+
+constexpr int kChunkTileForWorkspace = 32;  // smallest tile any variant uses
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+template <typename T, int D, int TILE_T, int STAGES, int NCW>
+static int launch_decode(DecodeParams p, void* out, void* workspace, size_t workspace_bytes, void* stream) {
+    using Cfg = DecodeCfg<T, D, TILE_T, STAGES, NCW>;
+    auto kernel = decode_split_kernel<T, D, TILE_T, STAGES, NCW>;
+    static bool configured[64] = {false};
+    static int ctas_per_sm[64] = {0};
+    int dev = 0;
+    B2KV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
+    if (!configured[dev]) {
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(Cfg::kSmemBytes)));
+        int occ = 0;
+        B2KV_CUDA_TRY(
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, Cfg::kThreads, Cfg::kSmemBytes));
+        if (occ < 1) return B2KV_ERR_UNSUPPORTED;
+        ctas_per_sm[dev] = occ;
+        configured[dev] = true;
+    }
+    int per_sm = tune_get("decode_grid_per_sm");
+    if (per_sm <= 0 || per_sm > ctas_per_sm[dev]) per_sm = ctas_per_sm[dev];
+    const int grid_full = device_sm_count() * per_sm;
+
+    p.chunk = pick_chunk(p.B, p.H, p.T_upper, TILE_T, grid_full);
+    p.c_max = (p.T_upper + p.chunk - 1) / p.chunk;
+    // a bulk copy may cover several rows only when rows are adjacent in memory
+    if (p.stride_t == D) {
+        p.run_len = p.block_table ? (p.block_size < TILE_T ? p.block_size : TILE_T) : TILE_T;
+        if (p.block_table && (TILE_T % p.run_len) != 0) p.run_len = 1;
+        if (p.block_table && p.block_size > TILE_T && (p.block_size % TILE_T) != 0) p.run_len = 1;
+    } else {
+        p.run_len = 1;
+    }
+    if (p.block_table && p.run_len > 1 && (p.chunk % p.run_len) != 0) p.run_len = 1;
+
+    const size_t slots = static_cast<size_t>(p.B) * p.H * p.c_max;
+    const size_t acc_bytes = align_up(slots * D * sizeof(float), 256);
+    const size_t need = acc_bytes + slots * 2 * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return B2KV_ERR_WORKSPACE;
+    p.ws_acc = static_cast<float*>(workspace);
+    p.ws_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
+
+    long long items_upper = static_cast<long long>(p.B) * p.H * p.c_max;
+    int grid = static_cast<int>(items_upper < grid_full ? items_upper : grid_full);
+    if (grid < 1) grid = 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(p);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    decode_combine_kernel<T, D><<<p.B * p.H, D, 0, s>>>(p, static_cast<T*>(out));
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
+template <typename T, int D>
+static int dispatch_variant(const DecodeParams& p, void* out, void* ws, size_t ws_bytes, void* stream) {
+    // Variants of the ring for the headline shape (256-byte rows); other shapes use the default.
+    if constexpr (D * sizeof(T) == 256) {
+        switch (tune_get("decode_variant")) {
+            case 1: return launch_decode<T, D, 64, 3, 4>(p, out, ws, ws_bytes, stream);
+            case 2: return launch_decode<T, D, 32, 4, 4>(p, out, ws, ws_bytes, stream);
+            case 3: return launch_decode<T, D, 64, 4, 8>(p, out, ws, ws_bytes, stream);
+            case 4: return launch_decode<T, D, 128, 3, 8>(p, out, ws, ws_bytes, stream);
+            case 5: return launch_decode<T, D, 32, 6, 4>(p, out, ws, ws_bytes, stream);
+            case 6: return launch_decode<T, D, 64, 6, 4>(p, out, ws, ws_bytes, stream);
+            default: return launch_decode<T, D, 64, 4, 4>(p, out, ws, ws_bytes, stream);
+        }
+    } else {
+        return launch_decode<T, D, 64, 4, 4>(p, out, ws, ws_bytes, stream);
+    }
+}
+
+template <typename T>
+static int dispatch_dim(const DecodeParams& p, int D, void* out, void* ws, size_t ws_bytes, void* stream) {
+    switch (D) {
+        case 16: return dispatch_variant<T, 16>(p, out, ws, ws_bytes, stream);
+        case 32: return dispatch_variant<T, 32>(p, out, ws, ws_bytes, stream);
+        case 64: return dispatch_variant<T, 64>(p, out, ws, ws_bytes, stream);
+        case 128: return dispatch_variant<T, 128>(p, out, ws, ws_bytes, stream);
+        case 256: return dispatch_variant<T, 256>(p, out, ws, ws_bytes, stream);
+        default: return B2KV_ERR_UNSUPPORTED;
+    }
+}
+
+static int decode_entry(const void* q, const void* k, const void* v, void* out, const int32_t* seq_lens, int len,
+                        int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
+                        int H, int D, int T_upper, int64_t s0, int64_t st, int64_t sh, int dtype, void* workspace,
+                        size_t workspace_bytes, int32_t* dev_status, void* stream) {
+    const int es = elt_bytes(dtype);
+    if (es == 0) return B2KV_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !out) return B2KV_ERR_BAD_ARG;
+    if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0) return B2KV_ERR_BAD_ARG;
+    if (static_cast<long long>(B) * H > 0x7fffffffLL / 4) return B2KV_ERR_UNSUPPORTED;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(workspace))
+        return B2KV_ERR_ALIGN;
+    if (!stride_ok(s0, es) || !stride_ok(st, es) || !stride_ok(sh, es)) return B2KV_ERR_ALIGN;
+    if (st < D && st != 0) return B2KV_ERR_BAD_ARG;
+    if (block_table && (max_blocks <= 0 || block_size <= 0 || n_blocks <= 0 ||
+                        static_cast<long long>(max_blocks) * block_size < T_upper))
+        return B2KV_ERR_BAD_ARG;
+    DecodeParams p{};
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.seq_lens = seq_lens;
+    p.block_table = block_table;
+    p.dev_status = dev_status;
+    p.len_scalar = len;
+    p.len_bias = len_bias;
+    p.B = B;
+    p.H = H;
+    p.T_upper = T_upper;
+    p.max_blocks = max_blocks;
+    p.block_size = block_size;
+    p.n_blocks = n_blocks;
+    p.stride_b = s0;
+    p.stride_t = st;
+    p.stride_h = sh;
+    p.q_prescale = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D)));
+    if (dtype == B2KV_DTYPE_F32) return dispatch_dim<float>(p, D, out, workspace, workspace_bytes, stream);
+    return dispatch_dim<__nv_bfloat16>(p, D, out, workspace, workspace_bytes, stream);
+}
+
+}  // namespace b2kv
+
+using namespace b2kv;
+
+extern "C" {
+
+size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper) {
+    if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0) return 0;
+    // sized for the smallest split any variant may choose (one tile of the smallest tile size)
+    const size_t c_max = (static_cast<size_t>(T_upper) + kChunkTileForWorkspace - 1) / kChunkTileForWorkspace;
+    const size_t slots = static_cast<size_t>(B) * H * c_max;
+    return align_up(slots * D * sizeof(float), 256) + slots * 2 * sizeof(float) + 256;
+}
+
+int b2kv_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens, int len,
+                int len_bias, int B, int H, int D, int T_upper, int64_t stride_b, int64_t stride_t, int64_t stride_h,
+                int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream) {
+    return decode_entry(q, k_cache, v_cache, out, seq_lens, len, len_bias, nullptr, 0, 0, 0, B, H, D, T_upper,
+                        stride_b, stride_t, stride_h, dtype, workspace, workspace_bytes, dev_status, stream);
+}
+
+int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, void* out, const int32_t* seq_lens,
+                      int len, int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks,
+                      int B, int H, int D, int T_upper, int64_t stride_blk, int64_t stride_t, int64_t stride_h,
+                      int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream) {
+    if (!block_table) return B2KV_ERR_BAD_ARG;
+    return decode_entry(q, k_pool, v_pool, out, seq_lens, len, len_bias, block_table, max_blocks, block_size,
+                        n_blocks, B, H, D, T_upper, stride_blk, stride_t, stride_h, dtype, workspace, workspace_bytes,
+                        dev_status, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,27 @@
+// Arguments shared by the two prefill kernels (SIMT and tensor core).
+#pragma once
+
+#include "b2kv_common.cuh"
+
+namespace b2kv {
+
+struct PrefillParams {
+    const void* Q;
+    const void* K;
+    const void* V;
+    void* O;
+    float* L;
+    float* M;
+    void* k_cache;
+    void* v_cache;
+    int64_t stride_b, stride_t, stride_h;
+    int B, N, H;
+    float q_prescale;
+};
+
+// SIMT kernel: every supported head_dim and storage type.
+int prefill_simt(const PrefillParams& p, int D, int dtype, void* stream);
+// Tensor-core kernel: returns B2KV_ERR_UNSUPPORTED when the shape is not one it takes.
+int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream);
+
+}  // namespace b2kv

@@ -1,0 +1,245 @@
+// Causal flash-attention prefill, SIMT version: any supported head_dim, fp32 or bf16 storage,
+// fp32 arithmetic.  It serves the shapes that the tensor-core kernel does not take (fp32
+// data, head_dim other than 128) and is the numerical cross-check of that kernel.
+//
+// Same tiling idea as the reference kernel (simple-llm/src/gpu/gpu_kernels.py:499-770): a
+// CTA owns a block of query rows of one (sequence, head) and walks the K/V blocks up to the
+// diagonal with an online softmax.  Differences: 32x32 tiles; each warp owns 8 query rows
+// for all three phases (scores, softmax, P.V), so only the K/V tile loads need a CTA-wide
+// barrier; the running (m, l) and the output accumulators live in registers; scores are
+// kept in the log2 domain.  L and M are written as the reference writes them (:762-768):
+// L = sum of exp(s - max), M = max of the scaled scores.
+// Optionally copies the K / V rows of the CTA's query block into the cache (bit-exact).
+#include <math.h>
+
+#include "b2kv_common.cuh"
+#include "prefill.cuh"
+
+namespace b2kv {
+
+
+constexpr int kBr = 32, kBc = 32, kPrefillThreads = 128, kRowsPerWarpP = 8;
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPrefillThreads) prefill_simt_kernel(const PrefillParams p) {
+    constexpr int KS = D + 4;  // padded K row (floats): 16-byte reads of 8 lanes hit distinct banks
+    constexpr int DPL = (D + 31) / 32;
+    constexpr int EPC = Elt<T>::kPerChunk;
+    constexpr int CPR = D / EPC;  // 16-byte chunks per row
+    extern __shared__ __align__(16) float smem_f[];
+    float* Qs = smem_f;             // [kBr][D]
+    float* Ks = Qs + kBr * D;       // [kBc][KS]
+    float* Vs = Ks + kBc * KS;      // [kBc][D]
+    float* Ss = Vs + kBc * D;       // [kBr][kBc + 1]
+
+    const int nqb = (p.N + kBr - 1) / kBr;
+    const int qb = nqb - 1 - blockIdx.x;  // longest rows first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int E = p.H * D;
+    const int q_start = qb * kBr;
+    const int q_end = min(q_start + kBr, p.N);
+    const T* Qg = static_cast<const T*>(p.Q) + static_cast<size_t>(b) * p.N * E + static_cast<size_t>(h) * D;
+    const T* Kg = static_cast<const T*>(p.K) + static_cast<size_t>(b) * p.N * E + static_cast<size_t>(h) * D;
+    const T* Vg = static_cast<const T*>(p.V) + static_cast<size_t>(b) * p.N * E + static_cast<size_t>(h) * D;
+
+    // Q block -> shared, pre-scaled; rows past N are zero
+    for (int i = tid; i < kBr * CPR; i += kPrefillThreads) {
+        const int r = i / CPR, c = i - r * CPR;
+        float f[EPC];
+        if (q_start + r < p.N) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(Qg + static_cast<size_t>(q_start + r) * E + c * EPC);
+            Elt<T>::widen(raw, f);
+        } else {
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) f[e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) Qs[r * D + c * EPC + e] = f[e] * p.q_prescale;
+    }
+
+    float m[kRowsPerWarpP], l[kRowsPerWarpP], acc[kRowsPerWarpP][DPL];
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarpP; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) acc[i][k] = 0.f;
+    }
+    const int r0 = warp * kRowsPerWarpP;  // this warp's rows inside the block
+
+    const int n_kv = (q_end - 1) / kBc + 1;  // K/V blocks that hold a visible key
+    for (int jb = 0; jb < n_kv; ++jb) {
+        const int kv_start = jb * kBc;
+        __syncthreads();  // previous tile fully used (and Q stored, first time round)
+        for (int i = tid; i < kBc * CPR; i += kPrefillThreads) {
+            const int r = i / CPR, c = i - r * CPR;
+            float kf[EPC], vf[EPC];
+            if (kv_start + r < p.N) {
+                const size_t off = static_cast<size_t>(kv_start + r) * E + c * EPC;
+                Elt<T>::widen(*reinterpret_cast<const uint4*>(Kg + off), kf);
+                Elt<T>::widen(*reinterpret_cast<const uint4*>(Vg + off), vf);
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) kf[e] = vf[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) {
+                Ks[r * KS + c * EPC + e] = kf[e];
+                Vs[r * D + c * EPC + e] = vf[e];
+            }
+        }
+        __syncthreads();
+
+        // scores: lane = key column, 8 query rows of this warp
+        float s[kRowsPerWarpP];
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarpP; ++i) s[i] = 0.f;
+        for (int d = 0; d < D; d += 4) {
+            const float4 kk = *reinterpret_cast<const float4*>(&Ks[lane * KS + d]);
+#pragma unroll
+            for (int i = 0; i < kRowsPerWarpP; ++i) {
+                const float4 qq = *reinterpret_cast<const float4*>(&Qs[(r0 + i) * D + d]);
+                s[i] = fmaf(qq.x, kk.x, s[i]);
+                s[i] = fmaf(qq.y, kk.y, s[i]);
+                s[i] = fmaf(qq.z, kk.z, s[i]);
+                s[i] = fmaf(qq.w, kk.w, s[i]);
+            }
+        }
+        // online softmax per row; P goes to shared for the P.V phase
+        const int key = kv_start + lane;
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarpP; ++i) {
+            const int row = q_start + r0 + i;
+            const bool visible = (key <= row) && (key < p.N);
+            float sv = visible ? s[i] : -INFINITY;
+            float mx = sv;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            const float m_new = fmaxf(m[i], mx);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float pr = exp2f(sv - m_use);
+            float sum = pr;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            const float corr = exp2f(m[i] - m_use);
+            l[i] = l[i] * corr + sum;
+            m[i] = m_new;
+#pragma unroll
+            for (int k = 0; k < DPL; ++k) acc[i][k] *= corr;
+            Ss[(r0 + i) * (kBc + 1) + lane] = pr;
+        }
+        __syncwarp();
+        // P.V: lane = output column (d = lane + 32k)
+        for (int c = 0; c < kBc; ++c) {
+            float vv[DPL];
+#pragma unroll
+            for (int k = 0; k < DPL; ++k) {
+                const int d = lane + 32 * k;
+                vv[k] = (d < D) ? Vs[c * D + d] : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < kRowsPerWarpP; ++i) {
+                const float pr = Ss[(r0 + i) * (kBc + 1) + c];
+#pragma unroll
+                for (int k = 0; k < DPL; ++k) acc[i][k] = fmaf(pr, vv[k], acc[i][k]);
+            }
+        }
+        __syncwarp();
+    }
+
+    // epilogue: O = acc / max(l, 1e-8), statistics, optional cache rows
+    T* Og = static_cast<T*>(p.O) + static_cast<size_t>(b) * p.N * E + static_cast<size_t>(h) * D;
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarpP; ++i) {
+        const int row = q_start + r0 + i;
+        if (row >= p.N) continue;
+        const float inv = 1.f / fmaxf(l[i], 1e-8f);
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) {
+            const int d = lane + 32 * k;
+            if (d < D) Og[static_cast<size_t>(row) * E + d] = Elt<T>::from_float(acc[i][k] * inv);
+        }
+        if (lane == 0) {
+            const size_t sidx = (static_cast<size_t>(b) * p.N + row) * p.H + h;
+            if (p.L) p.L[sidx] = l[i];
+            if (p.M) p.M[sidx] = m[i] * 0.6931471805599453f;  // back from the log2 domain
+        }
+    }
+    if (p.k_cache != nullptr) {
+        T* kc = static_cast<T*>(p.k_cache);
+        T* vc = static_cast<T*>(p.v_cache);
+        for (int i = tid; i < (q_end - q_start) * CPR; i += kPrefillThreads) {
+            const int r = i / CPR, c = i - r * CPR;
+            const size_t src = static_cast<size_t>(q_start + r) * E + c * EPC;
+            const int64_t dst = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(q_start + r) * p.stride_t +
+                                static_cast<int64_t>(h) * p.stride_h + c * EPC;
+            *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(Kg + src);
+            *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(Vg + src);
+        }
+    }
+}
+
+template <typename T, int D>
+static int launch_prefill_simt(const PrefillParams& p, void* stream) {
+    constexpr size_t smem = (static_cast<size_t>(kBr) * D + kBc * (D + 4) + kBc * D + kBr * (kBc + 1)) * sizeof(float);
+    auto kernel = prefill_simt_kernel<T, D>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    B2KV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
+    if (!configured[dev]) {
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured[dev] = true;
+    }
+    if (p.H > 65535 || p.B > 65535) return B2KV_ERR_UNSUPPORTED;
+    dim3 grid((p.N + kBr - 1) / kBr, p.H, p.B);
+    kernel<<<grid, kPrefillThreads, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
+template <typename T>
+static int dispatch_prefill_simt(const PrefillParams& p, int D, void* stream) {
+    switch (D) {
+        case 16: return launch_prefill_simt<T, 16>(p, stream);
+        case 32: return launch_prefill_simt<T, 32>(p, stream);
+        case 64: return launch_prefill_simt<T, 64>(p, stream);
+        case 128: return launch_prefill_simt<T, 128>(p, stream);
+        case 256: return launch_prefill_simt<T, 256>(p, stream);
+        default: return B2KV_ERR_UNSUPPORTED;
+    }
+}
+
+int prefill_simt(const PrefillParams& p, int D, int dtype, void* stream) {
+    if (dtype == B2KV_DTYPE_F32) return dispatch_prefill_simt<float>(p, D, stream);
+    return dispatch_prefill_simt<__nv_bfloat16>(p, D, stream);
+}
+
+}  // namespace b2kv
+
+using namespace b2kv;
+
+extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache,
+                            void* v_cache, int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B,
+                            int N, int H, int D, int dtype, void* stream) {
+    const int es = elt_bytes(dtype);
+    if (es == 0) return B2KV_ERR_UNSUPPORTED;
+    if (!Q || !K || !V || !O) return B2KV_ERR_BAD_ARG;
+    if (B <= 0 || N <= 0 || H <= 0 || D <= 0) return B2KV_ERR_BAD_ARG;
+    if ((k_cache == nullptr) != (v_cache == nullptr)) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O) || !aligned16(k_cache) || !aligned16(v_cache))
+        return B2KV_ERR_ALIGN;
+    if ((D * es) % 16 != 0) return B2KV_ERR_UNSUPPORTED;
+    if (k_cache) {
+        if (N > T_max) return B2KV_ERR_BAD_ARG;
+        if (!stride_ok(stride_b, es) || !stride_ok(stride_t, es) || !stride_ok(stride_h, es)) return B2KV_ERR_ALIGN;
+    }
+    PrefillParams p{Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, B, N, H,
+                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D)))};
+    if (!tune_get("prefill_force_simt")) {
+        int rc = prefill_tensor_core(p, D, dtype, stream);
+        if (rc != B2KV_ERR_UNSUPPORTED) return rc;
+    }
+    return prefill_simt(p, D, dtype, stream);
+}

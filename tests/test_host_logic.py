@@ -1,0 +1,133 @@
+"""Host-side behaviour of the reference API mirror, on CPU tensors: the same checks, texts
+and state changes as simple-llm/src/gpu/gpu_kv_cache.py and gpu_ops.py, exercised up to (not
+including) the kernel launch."""
+import pytest
+import torch
+
+
+@pytest.fixture()
+def ctx(pkg):
+    gpu = pkg.gpu
+    return gpu.GPUContext(device=torch.device("cpu"), config=gpu.GPUConfig(), batch_state=None)
+
+
+def _cfg(gpu, **kw):
+    base = dict(batch_size=2, max_seq_len=8, n_layers=2, n_heads=2, head_dim=16)
+    base.update(kw)
+    return gpu.KVCacheConfig(**base)
+
+
+def test_create_validates_dimensions_like_the_reference(pkg, ctx):
+    gpu = pkg.gpu
+    for field in ["batch_size", "max_seq_len", "n_layers", "n_heads", "head_dim"]:
+        with pytest.raises(ValueError, match=f"{field} must be > 0, got 0"):
+            gpu.kv_cache_create(ctx, _cfg(gpu, **{field: 0}))
+    with pytest.raises(ValueError, match="layout"):
+        gpu.kv_cache_create(ctx, _cfg(gpu, layout="htbd"))
+
+
+def test_create_shapes_and_zero_fill(pkg, ctx):
+    gpu = pkg.gpu
+    cache = gpu.kv_cache_create(ctx, _cfg(gpu))
+    assert len(cache.layers) == 2 and cache.current_len == 0
+    assert cache.layers[0].k_cache.shape == (2 * 8, 2 * 16)  # [B*T_max, H*D] as the reference
+    assert float(cache.layers[1].v_cache.buffer.abs().sum()) == 0.0
+    bhtd = gpu.kv_cache_create(ctx, _cfg(gpu, layout="bhtd", dtype=torch.bfloat16))
+    assert bhtd.layers[0].k_cache.shape == (2 * 2 * 8, 16) and bhtd.layers[0].k_cache.buffer.dtype == torch.bfloat16
+    paged = gpu.kv_cache_create(ctx, _cfg(gpu, block_size=4, n_blocks=10, ragged=True))
+    assert paged.block_table.shape == (2, 2) and paged.layers[0].k_cache.shape == (10 * 2 * 4, 16)
+    assert paged.seq_lens.tolist() == [0, 0]
+    with pytest.raises(ValueError, match="n_blocks"):
+        gpu.kv_cache_create(ctx, _cfg(gpu, block_size=4, n_blocks=3))
+
+
+def test_reset_and_set_lengths(pkg, ctx):
+    gpu = pkg.gpu
+    cache = gpu.kv_cache_create(ctx, _cfg(gpu, ragged=True))
+    cache.current_len = 5
+    gpu.kv_cache_reset(cache)
+    assert cache.current_len == 0
+    gpu.kv_cache_set_lengths(cache, [3, 7])
+    assert cache.current_len == 7 and cache.seq_lens.tolist() == [3, 7]
+    with pytest.raises(ValueError):
+        gpu.kv_cache_set_lengths(cache, [3, 9])
+
+
+def test_update_checks_fire_before_the_launch(pkg, ctx):
+    gpu = pkg.gpu
+    cache = gpu.kv_cache_create(ctx, _cfg(gpu))
+    good = gpu.gpu_buffer_2d_create(ctx, 2, 32)
+    with pytest.raises(ValueError, match=r"layer_idx 2 out of range \[0, 2\)"):
+        gpu.kv_cache_update(ctx, cache, 2, good, good)
+    cache.current_len = 8
+    with pytest.raises(ValueError, match="Cache is full: current_len=8, max_seq_len=8"):
+        gpu.kv_cache_update(ctx, cache, 0, good, good)
+    cache.current_len = 0
+    bad = gpu.gpu_buffer_2d_create(ctx, 2, 16)
+    with pytest.raises(ValueError, match="new_k shape mismatch"):
+        gpu.kv_cache_update(ctx, cache, 0, bad, good)
+    with pytest.raises(ValueError, match="new_v shape mismatch"):
+        gpu.kv_cache_update(ctx, cache, 0, good, bad)
+    # no open batch: the operation is refused on the host
+    with pytest.raises(RuntimeError, match="batch_begin"):
+        gpu.kv_cache_update(ctx, cache, 0, good, good)
+    assert cache.current_len == 0
+
+
+def test_attention_checks(pkg, ctx):
+    gpu = pkg.gpu
+    cache = gpu.kv_cache_create(ctx, _cfg(gpu, max_seq_len=512))
+    q = gpu.gpu_buffer_2d_create(ctx, 2, 32)
+    with pytest.raises(ValueError, match="Cache is empty: current_len=0"):
+        gpu.attention_with_kv_cache(ctx, cache, 0, q, q)
+    cache.current_len = 3
+    with pytest.raises(ValueError, match="out of range"):
+        gpu.attention_with_kv_cache(ctx, cache, -1, q, q)
+    with pytest.raises(ValueError, match="q_new shape mismatch"):
+        gpu.attention_with_kv_cache(ctx, cache, 0, gpu.gpu_buffer_2d_create(ctx, 2, 31), q)
+    with pytest.raises(ValueError, match="output shape mismatch"):
+        gpu.attention_with_kv_cache(ctx, cache, 0, q, gpu.gpu_buffer_2d_create(ctx, 1, 32))
+    # the reference's 256-token limit is opt-in
+    cache.current_len = 300
+    ctx.config.enforce_reference_decode_limit = True
+    with pytest.raises(ValueError, match=r"current_len \(300\) exceeds maximum supported"):
+        gpu.attention_with_kv_cache(ctx, cache, 0, q, q)
+
+
+def test_flash_attention_checks(pkg, ctx):
+    gpu = pkg.gpu
+    mk = lambda r, c: gpu.gpu_buffer_2d_create(ctx, r, c)  # noqa: E731
+    Q = mk(8, 32)
+    L = gpu.gpu_buffer_1d_create(ctx, 16)
+    ctx.config.flash_attn_max_head_dim = 8
+    with pytest.raises(ValueError, match="head_dim 16 exceeds maximum supported by config: 8"):
+        gpu.flash_attention(ctx, Q, Q, Q, Q, L, L, 2, 4, 2, 16)
+    ctx.config.flash_attn_max_head_dim = 128
+    with pytest.raises(ValueError, match="Invalid dimensions"):
+        gpu.flash_attention(ctx, Q, Q, Q, Q, L, L, 0, 4, 2, 16)
+    with pytest.raises(ValueError, match="K shape mismatch"):
+        gpu.flash_attention(ctx, Q, mk(8, 16), Q, Q, L, L, 2, 4, 2, 16)
+    with pytest.raises(ValueError, match="L shape mismatch"):
+        gpu.flash_attention(ctx, Q, Q, Q, Q, gpu.gpu_buffer_1d_create(ctx, 8), L, 2, 4, 2, 16)
+
+
+def test_batch_rules(pkg, ctx):
+    gpu = pkg.gpu
+    with pytest.raises(RuntimeError, match="Batch already submitted or not initialized"):
+        gpu.batch_commit(ctx)
+
+
+def test_buffer_helpers(pkg, ctx):
+    import numpy as np
+
+    gpu = pkg.gpu
+    with pytest.raises(ValueError, match="Buffer dimensions must be positive"):
+        gpu.gpu_buffer_2d_create(ctx, 0, 4)
+    with pytest.raises(ValueError, match="Buffer size must be positive"):
+        gpu.gpu_buffer_1d_create(ctx, 0)
+    with pytest.raises(ValueError, match="doesn't match buffer shape"):
+        gpu.gpu_buffer_2d_create(ctx, 2, 2, np.zeros((2, 3), dtype=np.float32))
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        gpu.gpu_buffer_2d_create(ctx, 2, 2, np.zeros((2, 2), dtype=np.float64))
+    buf = gpu.gpu_buffer_2d_create(ctx, 2, 2, np.arange(4, dtype=np.float32).reshape(2, 2))
+    assert buf.shape == (2, 2) and buf.size == 4
