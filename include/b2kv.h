@@ -111,7 +111,7 @@ int b2kv_gather_paged(const void* pool, void* out, const int32_t* seq_lens, int 
  * `workspace` is scratch of at least b2kv_decode_workspace_bytes(...) bytes; it needs no
  * initialisation and carries nothing between calls.
  */
-size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper);
+size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype);
 int b2kv_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens, int len,
                 int len_bias, int B, int H, int D, int T_upper, int64_t stride_b, int64_t stride_t, int64_t stride_h,
                 int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream);

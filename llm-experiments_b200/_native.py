@@ -41,7 +41,7 @@ SIGNATURES = {
                                _vp, _vp]),
     "b2kv_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
     "b2kv_gather_paged": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
-    "b2kv_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "b2kv_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "b2kv_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _sz, _vp, _vp]),
     "b2kv_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64,
                                _i, _vp, _sz, _vp, _vp]),

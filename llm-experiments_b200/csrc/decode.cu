@@ -421,19 +421,29 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeParams p,
 // host side
 // --------------------------------------------------------------------------------------
 
-static int pick_chunk(int B, int H, int T_upper, int tile, int grid_ctas) {
+// Tokens per K (or V) tile for a row of `row_bytes` in the generic configuration: 8 KB tiles,
+// so that several CTAs (twelve or more consumer warps) fit on one SM; the consumers, not the
+// copy engine, are what has to keep up with HBM.
+constexpr int default_tile(int row_bytes) {
+    int t = 8192 / row_bytes;
+    return t > 128 ? 128 : (t < 8 ? 8 : t);
+}
+// Smallest tile of any compiled variant for that row size (sizes the workspace).
+constexpr int smallest_tile(int row_bytes) { return row_bytes == 256 ? 16 : default_tile(row_bytes); }
+
+static int pick_chunk(int B, int H, int T_upper, int tile, int row_bytes, int grid_ctas) {
     int forced = tune_get("decode_chunk");
     if (forced > 0) return ((forced + tile - 1) / tile) * tile;
-    // enough items to give every resident CTA several, but items long enough to amortise
-    // the per-item merge: between one tile and eight tiles.
+    // Enough items to give every resident CTA several, but items long enough to amortise the
+    // per-item merge: between one tile and 256 KB of K rows.
     long long tiles_total = static_cast<long long>(B) * H * ((T_upper + tile - 1) / tile);
     long long per = tiles_total / (4ll * grid_ctas);
+    long long cap = (262144 / row_bytes) / tile;
+    if (cap < 1) cap = 1;
+    if (per > cap) per = cap;
     if (per < 1) per = 1;
-    if (per > 8) per = 8;
     return static_cast<int>(per) * tile;
 }
-
-constexpr int kChunkTileForWorkspace = 32;  // smallest tile any variant uses
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -460,7 +470,7 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     if (per_sm <= 0 || per_sm > ctas_per_sm[dev]) per_sm = ctas_per_sm[dev];
     const int grid_full = device_sm_count() * per_sm;
 
-    p.chunk = pick_chunk(p.B, p.H, p.T_upper, TILE_T, grid_full);
+    p.chunk = pick_chunk(p.B, p.H, p.T_upper, TILE_T, Cfg::kRowBytes, grid_full);
     p.c_max = (p.T_upper + p.chunk - 1) / p.chunk;
     // a bulk copy may cover several rows only when rows are adjacent in memory
     if (p.stride_t == D) {
@@ -492,19 +502,32 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
 
 template <typename T, int D>
 static int dispatch_variant(const DecodeParams& p, void* out, void* ws, size_t ws_bytes, void* stream) {
-    // Variants of the ring for the headline shape (256-byte rows); other shapes use the default.
-    if constexpr (D * sizeof(T) == 256) {
+    constexpr int kRow = D * static_cast<int>(sizeof(T));
+    // Variants of the ring for the headline row size (256 bytes: bf16 head_dim 128, fp32 head_dim 64);
+    // other row sizes use the default (8 KB tiles, 4 stages, 4 consumer warps).
+    if constexpr (kRow == 256) {
         switch (tune_get("decode_variant")) {
             case 1: return launch_decode<T, D, 64, 3, 4>(p, out, ws, ws_bytes, stream);
-            case 2: return launch_decode<T, D, 32, 4, 4>(p, out, ws, ws_bytes, stream);
+            case 2: return launch_decode<T, D, 32, 3, 4>(p, out, ws, ws_bytes, stream);
             case 3: return launch_decode<T, D, 64, 4, 8>(p, out, ws, ws_bytes, stream);
             case 4: return launch_decode<T, D, 128, 3, 8>(p, out, ws, ws_bytes, stream);
             case 5: return launch_decode<T, D, 32, 6, 4>(p, out, ws, ws_bytes, stream);
-            case 6: return launch_decode<T, D, 64, 6, 4>(p, out, ws, ws_bytes, stream);
-            default: return launch_decode<T, D, 64, 4, 4>(p, out, ws, ws_bytes, stream);
+            case 6: return launch_decode<T, D, 64, 2, 8>(p, out, ws, ws_bytes, stream);
+            case 7: return launch_decode<T, D, 16, 6, 4>(p, out, ws, ws_bytes, stream);
+            case 8: return launch_decode<T, D, 32, 4, 8>(p, out, ws, ws_bytes, stream);
+            case 9: return launch_decode<T, D, 32, 4, 4>(p, out, ws, ws_bytes, stream);
+            case 10: return launch_decode<T, D, 32, 5, 4>(p, out, ws, ws_bytes, stream);
+            case 11: return launch_decode<T, D, 16, 4, 4>(p, out, ws, ws_bytes, stream);
+            case 12: return launch_decode<T, D, 32, 2, 4>(p, out, ws, ws_bytes, stream);
+            case 13: return launch_decode<T, D, 64, 2, 16>(p, out, ws, ws_bytes, stream);
+            case 14: return launch_decode<T, D, 128, 2, 16>(p, out, ws, ws_bytes, stream);
+            case 15: return launch_decode<T, D, 64, 3, 16>(p, out, ws, ws_bytes, stream);
+            case 16: return launch_decode<T, D, 128, 2, 8>(p, out, ws, ws_bytes, stream);
+            // default: 16 KB tiles, 3 stages, 8 consumer warps, two CTAs per SM (best of the sweep)
+            default: return launch_decode<T, D, 64, 3, 8>(p, out, ws, ws_bytes, stream);
         }
     } else {
-        return launch_decode<T, D, 64, 4, 4>(p, out, ws, ws_bytes, stream);
+        return launch_decode<T, D, default_tile(kRow), 4, 4>(p, out, ws, ws_bytes, stream);
     }
 }
 
@@ -565,10 +588,12 @@ using namespace b2kv;
 
 extern "C" {
 
-size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper) {
-    if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0) return 0;
+size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype) {
+    const int es = elt_bytes(dtype);
+    if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0 || es == 0 || (D * es) % 16 != 0) return 0;
     // sized for the smallest split any variant may choose (one tile of the smallest tile size)
-    const size_t c_max = (static_cast<size_t>(T_upper) + kChunkTileForWorkspace - 1) / kChunkTileForWorkspace;
+    const size_t tile = static_cast<size_t>(smallest_tile(D * es));
+    const size_t c_max = (static_cast<size_t>(T_upper) + tile - 1) / tile;
     const size_t slots = static_cast<size_t>(B) * H * c_max;
     return align_up(slots * D * sizeof(float), 256) + slots * 2 * sizeof(float) + 256;
 }

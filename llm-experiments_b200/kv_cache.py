@@ -154,7 +154,7 @@ def kv_cache_update(ctx: GPUContext, cache: KVCache, layer_idx: int, new_k: GPUB
 def decode_workspace(cache: KVCache) -> torch.Tensor:
     if cache.workspace is None:
         nbytes = _native.lib.b2kv_decode_workspace_bytes(cache.batch_size, cache.n_heads, cache.head_dim,
-                                                         cache.max_seq_len)
+                                                         cache.max_seq_len, dtype_code(cache.dtype))
         cache.workspace = torch.empty(nbytes, dtype=torch.uint8, device=cache.layers[0].k_cache.buffer.device)
     return cache.workspace
 

@@ -80,7 +80,8 @@ def test_argument_checks_return_before_any_launch(pkg):
 
 def test_workspace_size_grows_with_the_problem(pkg):
     lib = pkg._native.lib
-    small = lib.b2kv_decode_workspace_bytes(1, 4, 64, 256)
-    big = lib.b2kv_decode_workspace_bytes(64, 32, 128, 8192)
+    small = lib.b2kv_decode_workspace_bytes(1, 4, 64, 256, 0)
+    big = lib.b2kv_decode_workspace_bytes(64, 32, 128, 8192, 1)
     assert 0 < small < big
-    assert lib.b2kv_decode_workspace_bytes(0, 4, 64, 256) == 0
+    assert lib.b2kv_decode_workspace_bytes(0, 4, 64, 256, 0) == 0
+    assert lib.b2kv_decode_workspace_bytes(1, 4, 64, 256, 9) == 0

@@ -211,7 +211,8 @@ def test_decode_uniform_length_mode_matches_ragged_mode(pkg, ctx):
 
 
 @pytest.mark.parametrize("variant,chunk", [(0, 0), (0, 64), (0, 1024), (1, 0), (2, 0), (3, 0), (4, 128), (5, 32),
-                                           (6, 0)])
+                                           (6, 0), (7, 16), (8, 0), (9, 0), (10, 0), (11, 0), (12, 0), (13, 0), (14, 0), (15, 0),
+                                           (16, 0)])
 def test_decode_kernel_variants_agree_with_oracle(pkg, ctx, variant, chunk):
     pkg._native.tune("decode_variant", variant)
     pkg._native.tune("decode_chunk", chunk)

@@ -1,0 +1,87 @@
+"""GPU parity: causal flash-attention prefill against the fixtures made from the reference
+test's own math (simple-llm/src/gpu_test.py:743-868) and against the oracle, plus the fused
+cache write (bit-exact)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle, kv_oracle
+from tests import kv_util as U
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx(pkg):
+    return U.make_ctx(pkg)
+
+
+def _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, cache=None, stats=True):
+    gpu = pkg.gpu
+    ctx.config.flash_attn_max_head_dim = max(D, 128)
+    mk = lambda a: U.buf2d(pkg, ctx, a.reshape(B * N, H * D).contiguous())  # noqa: E731
+    Qb, Kb, Vb = mk(Q), mk(K), mk(V)
+    Ob = U.buf2d(pkg, ctx, torch.empty((B * N, H * D), dtype=dtype, device=ctx.device))
+    Lb = gpu.gpu_buffer_1d_create(ctx, B * N * H) if stats else None
+    Mb = gpu.gpu_buffer_1d_create(ctx, B * N * H) if stats else None
+    gpu.batch_begin(ctx)
+    gpu.flash_attention(ctx, Qb, Kb, Vb, Ob, Lb, Mb, B, N, H, D, cache=cache, layer_idx=0)
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    return Ob.buffer, (Lb.buffer if stats else None), (Mb.buffer if stats else None)
+
+
+@pytest.mark.parametrize("case", range(len(kv_oracle.FLASH_RECIPE_SHAPES)))
+def test_reference_flash_recipes(pkg, ctx, golden, case):
+    B, N, H, D = kv_oracle.FLASH_RECIPE_SHAPES[case]
+    Qn, Kn, Vn = kv_oracle.recipe_flash_inputs(B, N, H, D, seed=42)
+    dev = lambda a: torch.from_numpy(a).to(ctx.device)  # noqa: E731
+    O, L, M = _run_flash(pkg, ctx, dev(Qn), dev(Kn), dev(Vn), B, N, H, D, torch.float32)
+    np.testing.assert_allclose(O.cpu().numpy().reshape(B, N, H * D), golden[f"flash_out_{case}"], rtol=1e-4, atol=1e-5)
+    # L and M, which the reference writes but never checks: against the shader-order oracle
+    _, Lw, Mw = kv_oracle.flash_attention_tiled(Qn, Kn, Vn, B, N, H, D, Br=8, Bc=8)
+    np.testing.assert_allclose(L.cpu().numpy(), Lw, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(M.cpu().numpy(), Mw, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,N,H,D", [(2, 1, 2, 64), (1, 33, 3, 128), (2, 200, 2, 64), (1, 77, 2, 256), (2, 95, 4, 32),
+                                     (1, 129, 2, 16)])
+def test_prefill_ragged_shapes_vs_oracle(pkg, ctx, dtype, B, N, H, D):
+    Q = U.randn((B, N, H * D), dtype, ctx.device, 1)
+    K = U.randn((B, N, H * D), dtype, ctx.device, 2)
+    V = U.randn((B, N, H * D), dtype, ctx.device, 3)
+    O, L, M = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype)
+    Ow, Lw, Mw = c_oracle.prefill(U.to_oracle(Q.reshape(B * N, H * D)), U.to_oracle(K.reshape(B * N, H * D)),
+                                  U.to_oracle(V.reshape(B * N, H * D)), B, N, H, D)
+    np.testing.assert_allclose(U.to_f32(O), Ow, **U.TOL[dtype])
+    np.testing.assert_allclose(L.cpu().numpy(), Lw, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(M.cpu().numpy(), Mw, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 128), (torch.bfloat16, 64)])
+@pytest.mark.parametrize("layout", ["bthd", "bhtd"])
+def test_prefill_writes_cache_rows_bit_exact_then_decode_continues(pkg, ctx, dtype, D, layout):
+    gpu = pkg.gpu
+    B, N, H, T_max = 2, 150, 3, 256
+    E = H * D
+    Q = U.randn((B, N, E), dtype, ctx.device, 4)
+    K = U.randn((B, N, E), dtype, ctx.device, 5)
+    V = U.randn((B, N, E), dtype, ctx.device, 6)
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H,
+                                                       head_dim=D, dtype=dtype, layout=layout))
+    O, _, _ = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, cache=cache, stats=False)
+    assert cache.current_len == N
+    kview = U.logical_view(cache, cache.layers[0], "k")
+    vview = U.logical_view(cache, cache.layers[0], "v")
+    assert torch.equal(kview[:, :N].reshape(B, N, E), K) and torch.equal(vview[:, :N].reshape(B, N, E), V)
+    assert float(kview[:, N:].float().abs().sum()) == 0.0
+    # decoding the last prompt token over the prefilled cache reproduces the prefill's last row
+    q_last = Q[:, N - 1].contiguous()
+    out = torch.empty_like(q_last)
+    gpu.batch_begin(ctx)
+    gpu.attention_with_kv_cache(ctx, cache, 0, U.buf2d(pkg, ctx, q_last), U.buf2d(pkg, ctx, out))
+    gpu.batch_commit(ctx)
+    tol = U.TOL[dtype]
+    np.testing.assert_allclose(U.to_f32(out), U.to_f32(O.reshape(B, N, E)[:, N - 1]), rtol=max(tol["rtol"], 1e-4),
+                               atol=tol["atol"])
