@@ -52,6 +52,8 @@ extern "C" {
 #define B2KV_ERR_UNSUPPORTED (-3) /* head_dim / dtype / block_size combination not compiled  */
 #define B2KV_ERR_WORKSPACE (-4)   /* workspace missing or smaller than *_workspace_bytes     */
 #define B2KV_ERR_CUDA (-5)        /* a CUDA runtime call failed; see b2kv_last_cuda_error    */
+#define B2KV_ERR_STATIC_LIMIT (-6) /* b2kv_decode_static: the problem needs more scratch than
+                                      B2KV_STATIC_SCRATCH_BYTES                               */
 
 #define B2KV_DEV_BAD_BLOCK 1    /* block-table entry outside the pool           */
 #define B2KV_DEV_BAD_POSITION 2 /* append position outside [0, T_max)           */
@@ -119,6 +121,39 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
                       int len, int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks,
                       int B, int H, int D, int T_upper, int64_t stride_blk, int64_t stride_t, int64_t stride_h,
                       int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream);
+
+/*
+ * b2kv_decode without a workspace argument.  It has no counterpart in the reference, whose
+ * dispatch layer creates a fresh uniform buffer for every operation
+ * (simple-llm/src/gpu/gpu_ops.py:184-203, :298) and so always allocates.
+ *
+ * Who needs it: a caller that may not allocate device memory at the moment it decodes.  An
+ * inference server that handed every free byte of HBM to its KV-cache pool at start-up has
+ * nothing left for cudaMalloc to give; a decode loop with a latency budget cannot afford
+ * cudaMalloc either, because it synchronises the whole device and takes a process-wide lock.
+ * Such callers still pass q, the caches and out, but the split-K partials go to an array
+ * of B2KV_STATIC_SCRATCH_BYTES bytes that is part of the library image: every GPU whose
+ * context loads the library holds that much memory until the process exits.  The call itself
+ * performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *
+ * Limits and rules:
+ *   - Shapes whose partials do not fit (B * H * ceil(T_upper / split) * (D + 2) * 4 bytes with the
+ *     split the library chooses) are refused with B2KV_ERR_STATIC_LIMIT before anything is
+ *     launched; use b2kv_decode with your own workspace for those.  The benchmark shape
+ *     (B=64, H=32, D=128, T_upper <= 9216, bf16) needs about 10 MB.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call before starting
+ *     any stream capture on that device.
+ *   - All calls on one device share the one array and it keeps whatever the previous call left
+ *     in it.  Nothing in it has to start at zero (each call writes every slot before reading
+ *     it), but two calls that overlap on the GPU (different streams, no ordering between
+ *     them) race on it: keep calls on one device in stream order.
+ *   - Contiguous caches only (no block table).  Results are bit-identical to b2kv_decode.
+ */
+#define B2KV_STATIC_SCRATCH_BYTES (16u << 20)
+int b2kv_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens,
+                       int len, int len_bias, int B, int H, int D, int T_upper, int64_t stride_b, int64_t stride_t,
+                       int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
 
 /*
  * Causal flash-attention prefill.  Replaces flash_attention's dispatch

@@ -19,6 +19,8 @@ ERR_ALIGN = -2
 ERR_UNSUPPORTED = -3
 ERR_WORKSPACE = -4
 ERR_CUDA = -5
+ERR_STATIC_LIMIT = -6
+STATIC_SCRATCH_BYTES = 16 << 20
 
 DEV_STATUS_TEXT = {
     1: "a block-table entry points outside the pool",
@@ -45,6 +47,7 @@ SIGNATURES = {
     "b2kv_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _sz, _vp, _vp]),
     "b2kv_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64,
                                _i, _vp, _sz, _vp, _vp]),
+    "b2kv_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp]),
     "b2kv_tune": (_i, [ctypes.c_char_p, _i]),
 }

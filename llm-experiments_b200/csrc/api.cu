@@ -59,6 +59,9 @@ const char* b2kv_strerror(int status) {
         case B2KV_ERR_UNSUPPORTED: return "unsupported head_dim / dtype / block_size combination";
         case B2KV_ERR_WORKSPACE: return "workspace missing or too small";
         case B2KV_ERR_CUDA: return "CUDA runtime error (see b2kv_last_cuda_error)";
+        case B2KV_ERR_STATIC_LIMIT:
+            return "b2kv_decode_static: this shape needs more scratch than the built-in array holds "
+                   "(B2KV_STATIC_SCRATCH_BYTES); call b2kv_decode with a workspace instead";
         default: return "unknown status";
     }
 }

@@ -616,3 +616,46 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
 }
 
 }  // extern "C"
+
+// --------------------------------------------------------------------------------------
+// Decode without any allocation by the caller: the split-K partials live in an array that is
+// part of the library image.
+// --------------------------------------------------------------------------------------
+
+// Partials of b2kv_decode_static.  File scope, so every GPU whose context loads this library
+// holds these B2KV_STATIC_SCRATCH_BYTES until the process exits.  In host code this name is only
+// a host-side stand-in for the device array, never a device address: the address is obtained
+// with cudaGetSymbolAddress below and that pointer is what the kernels receive.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[B2KV_STATIC_SCRATCH_BYTES];
+
+// Device address of the array for the current device, looked up once per device.
+static int decode_static_scratch(void** out) {
+    static void* addr[64] = {nullptr};
+    int dev = 0;
+    B2KV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        B2KV_CUDA_TRY(cudaGetSymbolAddress(&p, g_decode_static_scratch));
+        if (p == nullptr) return B2KV_ERR_CUDA;
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return B2KV_OK;
+}
+
+extern "C" int b2kv_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                  const int32_t* seq_lens, int len, int len_bias, int B, int H, int D, int T_upper,
+                                  int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype,
+                                  int32_t* dev_status, void* stream) {
+    void* scratch = nullptr;
+    int rc = decode_static_scratch(&scratch);
+    if (rc != B2KV_OK) return rc;
+    // The partials need no clearing: every slot that the merge kernel reads is written by the
+    // split kernel of the same call first.
+    rc = decode_entry(q, k_cache, v_cache, out, seq_lens, len, len_bias, nullptr, 0, 0, 0, B, H, D, T_upper, stride_b,
+                      stride_t, stride_h, dtype, scratch, static_cast<size_t>(B2KV_STATIC_SCRATCH_BYTES), dev_status,
+                      stream);
+    return rc == B2KV_ERR_WORKSPACE ? B2KV_ERR_STATIC_LIMIT : rc;
+}
+
