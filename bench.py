@@ -42,6 +42,8 @@ WORKLOADS = {
     # name: (B, H, D, len_lo, len_hi, block_size, description)
     "decode": dict(B=64, H=32, D=128, lo=512, hi=8192, block_size=0,
                    desc="decode microbench: B=64 H=32 D=128 bf16, len~U[512,8192] seed 0, [B,H,T,D] cache"),
+    "decode_small": dict(B=8, H=32, D=128, lo=512, hi=8192, block_size=0,
+                         desc="decode microbench cut to 8 sequences (1.2 GB cache, for profiler captures)"),
     "paged": dict(B=64, H=32, D=128, lo=512, hi=8192, block_size=16,
                   desc="paged decode: same shapes, 16-token blocks placed by a seeded permutation of 65536 blocks"),
     "longctx": dict(B=4, H=64, D=128, lo=131072, hi=131072, block_size=0,
@@ -390,16 +392,19 @@ def run_b200(args, w, rank, world):
         "roofline": {"bound": "hbm", "kernel": "decode_split_kernel + decode_combine_kernel (one b2kv_decode call)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "frac_of_8000_nominal": achieved / 8000.0, "peak_kind": peak_kind, "ms_per_launch": ms_dec,
-                     "algorithmic_bytes_per_launch": dec_bytes, "traffic": DRAM_TRAFFIC_PER_LAUNCH.get(args.workload)},
+                     "algorithmic_bytes_per_launch": dec_bytes,
+                     "traffic": int(DRAM_BYTES_PER_TOKEN_HEAD * float(np.sum(lens0 + 1)) * H) if not bs else None},
         "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the split kernel from an ncu capture, scaled
-# to a full launch of the workload (see profiles/); None until captured.
-DRAM_TRAFFIC_PER_LAUNCH = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of the split kernel per attended (token, head), from
+# the ncu capture of the 8-sequence case (profiles/decode_split_kernel_decode_small.md: 413.2 MB for
+# 24908 tokens x 32 heads; the algorithmic figure is 512 B).  Traffic grows in proportion to the
+# tokens attended, so a full launch is this figure times its tokens and heads.
+DRAM_BYTES_PER_TOKEN_HEAD = 518.4
 
 
 def main():

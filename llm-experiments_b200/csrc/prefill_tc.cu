@@ -1,14 +1,488 @@
-// Causal flash-attention prefill on the tcgen05 tensor cores (bf16, head_dim 128).
+// Causal flash-attention prefill on the Blackwell tensor cores: bf16, head_dim 128.
+//
+// The reference kernel (simple-llm/src/gpu/gpu_kernels.py:499-770) computes the same tiled
+// online softmax with scalar fp32 dot products from workgroup memory.  Here QK^T and PV are
+// tcgen05.mma contractions with fp32 accumulators in tensor memory (TMEM):
+//
+//   * one CTA per (sequence, head, block of 128 query rows); 128-key K/V tiles up to the diagonal;
+//   * warp 4 issues TMA tiled loads (cp.async.bulk.tensor, 128-byte swizzle) of Q, K and V tiles
+//     into shared memory rings that complete on mbarriers;
+//   * warp 5 issues the MMAs from one thread: S = Q K^T (both operands K-major in shared memory)
+//     into one of two S buffers in TMEM, and O += P V with P read from TMEM (it overwrites the S
+//     buffer it was computed from) and V as an MN-major shared-memory operand.  QK^T of the next
+//     tile is issued before PV of the current one, so the tensor pipe works while the softmax runs;
+//   * warps 0-3 do the softmax: thread i owns query row i (= TMEM lane i), reads its S row with
+//     tcgen05.ld, keeps the running max / sum in registers in the log2 domain, writes P as packed
+//     bf16 with tcgen05.st.  O stays in TMEM for the whole row block and is rescaled only when a
+//     row's running max has grown by more than 2^8 since the last rescale (the factor cancels in
+//     O / l, so the result is the same);
+//   * epilogue: O / max(l, 1e-8) -> bf16, L and M as the reference writes them (:762-768), and the
+//     block's own K / V rows copied into the KV cache when one is given.
+//
+// Every mbarrier wait is bounded; a wait that runs out makes all warps fall through to the
+// common exit, where the tensor memory is released.
+#include <cuda.h>
+#include <math.h>
+
 #include "prefill.cuh"
 
 namespace b2kv {
 
+namespace tc {
+
+constexpr int kBlockM = 128;  // query rows per CTA
+constexpr int kBlockN = 128;  // keys per tile
+constexpr int kD = 128;
+constexpr int kKStages = 2, kVStages = 2;
+constexpr int kHalfTileBytes = 128 * 128;          // 128 rows x 64 bf16 (one 128-byte swizzle span per row)
+constexpr int kTileBytes = 2 * kHalfTileBytes;     // 128 x 128 bf16
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kColS0 = 0, kColS1 = 128, kColO = 256;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct SharedStorage {
+    alignas(1024) uint8_t q[kTileBytes];
+    alignas(1024) uint8_t k[kKStages][kTileBytes];
+    alignas(1024) uint8_t v[kVStages][kTileBytes];
+    alignas(8) uint64_t q_full;
+    uint64_t k_full[kKStages], k_empty[kKStages];
+    uint64_t v_full[kVStages], v_empty[kVStages];
+    uint64_t s_full[2], p_ready[2];
+    uint64_t o_done;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, int cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, int cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Arrives once on `bar` when every tcgen05 operation issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor: fp32 accumulate, bf16 A and B, M = N = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accum), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);  // .x = lo (low 16 bits), .y = hi
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage& sm =
+        *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_qb = (p.N + kBlockM - 1) / kBlockM;
+    // heaviest query blocks (most K/V tiles) first
+    const int qb = n_qb - 1 - static_cast<int>(blockIdx.x / (p.H * p.B));
+    const int bh = blockIdx.x % (p.H * p.B);
+    const int b = bh / p.H, h = bh % p.H;
+    const int q0 = qb * kBlockM;
+    const int n_tiles = qb + 1;  // causal: K/V tiles 0 .. qb
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < kKStages; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+        }
+        for (int s = 0; s < kVStages; ++s) {
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.s_full[s], 1);
+            mbar_init(&sm.p_ready[s], 128);
+        }
+        mbar_init(&sm.o_done, 1);
+        sm.abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(&sm.tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const int x0 = h * kD;
+            mbar_arrive_expect_tx(&sm.q_full, kTileBytes);
+            tma_load_3d(sm.q, &tm_q, &sm.q_full, x0, q0, b);
+            tma_load_3d(sm.q + kHalfTileBytes, &tm_q, &sm.q_full, x0 + 64, q0, b);
+            for (int j = 0; j < n_tiles && !sm.abort_flag; ++j) {
+                const int ks = j % kKStages, vs = j % kVStages;
+                if (!mbar_wait(&sm.k_empty[ks], ((j / kKStages) & 1) ^ 1)) {
+                    sm.abort_flag = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(&sm.k_full[ks], kTileBytes);
+                tma_load_3d(sm.k[ks], &tm_k, &sm.k_full[ks], x0, j * kBlockN, b);
+                tma_load_3d(sm.k[ks] + kHalfTileBytes, &tm_k, &sm.k_full[ks], x0 + 64, j * kBlockN, b);
+                if (!mbar_wait(&sm.v_empty[vs], ((j / kVStages) & 1) ^ 1)) {
+                    sm.abort_flag = 1;
+                    break;
+                }
+                mbar_arrive_expect_tx(&sm.v_full[vs], kTileBytes);
+                tma_load_3d(sm.v[vs], &tm_v, &sm.v_full[vs], x0, j * kBlockN, b);
+                tma_load_3d(sm.v[vs] + kHalfTileBytes, &tm_v, &sm.v_full[vs], x0 + 64, j * kBlockN, b);
+            }
+        }
+        __syncwarp();
+        // the block's own K / V rows -> cache (bit-exact copy), overlapped with the compute
+        if (p.k_cache != nullptr) {
+            const int E = p.H * kD;
+            const __nv_bfloat16* Kg = static_cast<const __nv_bfloat16*>(p.K) + static_cast<size_t>(b) * p.N * E + h * kD;
+            const __nv_bfloat16* Vg = static_cast<const __nv_bfloat16*>(p.V) + static_cast<size_t>(b) * p.N * E + h * kD;
+            __nv_bfloat16* kc = static_cast<__nv_bfloat16*>(p.k_cache);
+            __nv_bfloat16* vc = static_cast<__nv_bfloat16*>(p.v_cache);
+            const int rows = min(kBlockM, p.N - q0);
+            for (int i = lane; i < rows * 16; i += 32) {
+                const int r = i >> 4, c = i & 15;
+                const size_t src = static_cast<size_t>(q0 + r) * E + c * 8;
+                const int64_t dst = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(q0 + r) * p.stride_t +
+                                    static_cast<int64_t>(h) * p.stride_h + c * 8;
+                *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(Kg + src);
+                *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(Vg + src);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc(0, 0);
+            constexpr uint32_t idesc_pv = instr_desc(0, 1);
+            const uint32_t q_addr = smem_u32(sm.q);
+            bool ok = mbar_wait(&sm.q_full, 0);
+            auto issue_qk = [&](int j) {
+                const int ks = j % kKStages;
+                const uint32_t k_addr = smem_u32(sm.k[ks]);
+                const uint32_t s_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+#pragma unroll
+                for (int kb = 0; kb < 2; ++kb) {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint32_t off = kb * kHalfTileBytes + kk * 32;  // 16 bf16 of K = 32 bytes inside the span
+                        mma_ss(s_tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk,
+                               (kb | kk) ? 1u : 0u);
+                    }
+                }
+                mma_commit(&sm.s_full[j & 1]);
+                mma_commit(&sm.k_empty[ks]);
+            };
+            if (ok) ok = mbar_wait(&sm.k_full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    ok = mbar_wait(&sm.k_full[(j + 1) % kKStages], ((j + 1) / kKStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                const int vs = j % kVStages;
+                ok = mbar_wait(&sm.p_ready[j & 1], (j >> 1) & 1) && mbar_wait(&sm.v_full[vs], (j / kVStages) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sm.v[vs]);
+                const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    // 16 keys per step: 8 packed columns of P, 16 rows (2048 bytes) of V
+                    mma_ts(tmem + kColO, p_tmem + kk * 8, smem_desc(v_addr + kk * 2048, kHalfTileBytes, 1024), idesc_pv,
+                           (j | kk) ? 1u : 0u);
+                }
+                mma_commit(&sm.v_empty[vs]);
+                mma_commit(&sm.o_done);
+            }
+            if (!ok) sm.abort_flag = 1;
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ softmax: thread = query row ------------------------------
+        const int row = threadIdx.x;  // 0..127, also the TMEM lane
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const float c = p.q_prescale;  // log2(e) / sqrt(D)
+        float m_used = -INFINITY, m_run = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const uint32_t s_tmem = tmem + lane_base + ((j & 1) ? kColS1 : kColS0);
+            ok = mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const bool diag = (j == qb);
+            // pass 1: row maximum of the raw scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(s_tmem + cc * 32, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float s = __uint_as_float(r[i]);
+                    if (!diag || (cc * 32 + i) <= row) mx = fmaxf(mx, s);
+                }
+            }
+            const float mx_scaled = mx * c;
+            m_run = fmaxf(m_run, mx_scaled);
+            float factor = 1.f;
+            bool need = false;
+            if (j == 0) {
+                m_used = m_run;
+            } else if (m_run > m_used + kRescaleThreshold) {
+                factor = exp2f(m_used - m_run);
+                m_used = m_run;
+                need = true;
+            }
+            // pass 2: P = exp2(s*c - m_used) as packed bf16 over the first 64 columns of the S buffer
+            float sum = 0.f;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(s_tmem + cc * 32, r);
+                tmem_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), c, -m_used));
+                    float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), c, -m_used));
+                    if (diag) {
+                        if (cc * 32 + 2 * i > row) p0 = 0.f;
+                        if (cc * 32 + 2 * i + 1 > row) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    pk[i] = pack_bf16(p0, p1);
+                }
+                tmem_st16(s_tmem + cc * 16, pk);
+            }
+            l = l * factor + sum;
+            // rare: bring O down to the new reference maximum (needs PV of the previous tile finished)
+            if (__any_sync(0xffffffffu, need)) {
+                ok = mbar_wait(&sm.o_done, (j - 1) & 1);
+                if (ok) {
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int cc = 0; cc < 4; ++cc) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem + lane_base + kColO + cc * 32, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+                        tmem_st32(tmem + lane_base + kColO + cc * 32, r);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sm.p_ready[j & 1]);
+        }
+        if (ok) ok = mbar_wait(&sm.o_done, (n_tiles - 1) & 1);
+        if (ok) {
+            tc_fence_after();
+            const int grow = q0 + row;
+            const float inv = 1.f / fmaxf(l, 1e-8f);
+            const int E = p.H * kD;
+            __nv_bfloat16* Og =
+                static_cast<__nv_bfloat16*>(p.O) + (static_cast<size_t>(b) * p.N + grow) * E + static_cast<size_t>(h) * kD;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + kColO + cc * 32, r);
+                tmem_wait_ld();
+                if (grow < p.N) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(r[v4 * 8 + 0]) * inv, __uint_as_float(r[v4 * 8 + 1]) * inv);
+                        o.y = pack_bf16(__uint_as_float(r[v4 * 8 + 2]) * inv, __uint_as_float(r[v4 * 8 + 3]) * inv);
+                        o.z = pack_bf16(__uint_as_float(r[v4 * 8 + 4]) * inv, __uint_as_float(r[v4 * 8 + 5]) * inv);
+                        o.w = pack_bf16(__uint_as_float(r[v4 * 8 + 6]) * inv, __uint_as_float(r[v4 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(Og + cc * 32 + v4 * 8) = o;
+                    }
+                }
+            }
+            if (grow < p.N) {
+                const size_t sidx = (static_cast<size_t>(b) * p.N + grow) * p.H + h;
+                if (p.L) p.L[sidx] = l * exp2f(m_used - m_run);
+                if (p.M) p.M[sidx] = m_run * 0.6931471805599453f;
+            }
+        } else {
+            sm.abort_flag = 1;
+        }
+    }
+
+    // common exit: every warp arrives here, then the allocating warp releases the tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// View of a [B*N, H*D] bf16 matrix as (x = column, y = row inside the sequence, z = sequence), so
+// that rows past the end of a sequence read as zero instead of the next sequence's rows.
+static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(E), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(E) * 2, static_cast<cuuint64_t>(N) * E * 2};
+    const cuuint32_t box[3] = {64, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
 int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) {
-    (void)p;
-    (void)D;
-    (void)dtype;
-    (void)stream;
-    return B2KV_ERR_UNSUPPORTED;
+    if (dtype != B2KV_DTYPE_BF16 || D != tc::kD) return B2KV_ERR_UNSUPPORTED;
+    const int E = p.H * D;
+    const long long n_qb = (p.N + tc::kBlockM - 1) / tc::kBlockM;
+    const long long ctas = n_qb * p.H * p.B;
+    if (ctas > 0x7fffffffLL) return B2KV_ERR_UNSUPPORTED;
+    CUtensorMap tq, tk, tv;
+    if (!tc::make_map(&tq, p.Q, p.B, p.N, E) || !tc::make_map(&tk, p.K, p.B, p.N, E) ||
+        !tc::make_map(&tv, p.V, p.B, p.N, E))
+        return B2KV_ERR_UNSUPPORTED;  // no tensor-map encoder in this driver: the SIMT kernel takes over
+    constexpr size_t smem = sizeof(tc::SharedStorage) + 1024;
+    static bool configured[64] = {false};
+    int dev = 0;
+    B2KV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
+    if (!configured[dev]) {
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(tc::prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem)));
+        configured[dev] = true;
+    }
+    tc::prefill_tc_kernel<<<static_cast<unsigned>(ctas), tc::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv,
+                                                                                                                  p);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
 }
 
 }  // namespace b2kv
