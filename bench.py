@@ -48,6 +48,11 @@ WORKLOADS = {
                   desc="paged decode: same shapes, 16-token blocks placed by a seeded permutation of 65536 blocks"),
     "longctx": dict(B=4, H=64, D=128, lo=131072, hi=131072, block_size=0,
                     desc="long-context decode: B=4 H=64 D=128 bf16, len 131072, batch-resident on one GPU"),
+    "longctx_headsplit": dict(B=4, H=64, D=128, lo=131072, hi=131072, block_size=0, head_split=True,
+                              desc="long-context decode: B=4 H=64 D=128 bf16, len 131072, heads split over the "
+                                   "GPUs, outputs all-gathered with NCCL"),
+    "prefill": dict(B=8, H=32, D=128, N=4096, prefill=True,
+                    desc="causal prefill: B=8 H=32 D=128 N=4096 bf16, fused with the K/V cache write"),
 }
 SLACK = 1024  # rows of head-room above the longest sequence for the appended tokens
 
@@ -187,6 +192,8 @@ def cpu_port_run(w, lens, steps, warmup, sample_seqs, log=None):
 def run_reference(args, w, rank):
     if rank != 0:
         return
+    if w.get("prefill"):
+        w = WORKLOADS["decode"]  # the CPU arm times the decode step, the headline workload
     lens = make_lengths(w, 0)
     steps = max(1, args.steps)
     warm = max(1, min(args.warmup, 3))
@@ -238,9 +245,16 @@ def run_b200(args, w, rank, world):
     ctx = gpu.context_create(local_rank)
 
     B, H, D, bs = w["B"], w["H"], w["D"], w["block_size"]
+    head_split = bool(w.get("head_split"))
+    H_total = H
+    if head_split:
+        from llm_experiments_b200 import sharding
+
+        h0, h1 = sharding.head_range(H, rank, world)  # this rank's heads of every sequence
+        H = h1 - h0
     E = H * D
     dtype = torch.bfloat16
-    lens0 = make_lengths(w, rank)  # rank 0 draws the seed-0 lengths of the named config
+    lens0 = make_lengths(w, 0 if head_split else rank)  # rank 0 draws the seed-0 lengths of the named config
     T_max = int(lens0.max()) + SLACK
     n_blocks = 0
     if bs:
@@ -276,6 +290,8 @@ def run_b200(args, w, rank, world):
         gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
         gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
         gpu.batch_commit(ctx)
+        if head_split and world > 1:
+            sharding.gather_heads(out_dev)  # [B, H_total*D] on every rank
 
     def barrier():
         if world > 1:
@@ -311,7 +327,8 @@ def run_b200(args, w, rank, world):
     sampler.start()
     ms_total = timed(step_device, steps)
     ms_step = ms_total / steps
-    tokens_per_s = world * B / (ms_step * 1e-3)
+    seqs_total = B if head_split else world * B  # head split: the same B sequences on every rank
+    tokens_per_s = seqs_total / (ms_step * 1e-3)
 
     # ---- roofline: the decode call (split kernel + combine) alone, CUDA events ---------
     reset_lengths()
@@ -337,6 +354,7 @@ def run_b200(args, w, rank, world):
     nk_host = nk_dev.cpu().pin_memory()
     nv_host = nv_dev.cpu().pin_memory()
     out_host = torch.empty((B, E), dtype=dtype).pin_memory()
+    out_host_full = torch.empty((B, H_total * D), dtype=dtype).pin_memory()
 
     def step_e2e():
         gpu.gpu_buffer_2d_write(ctx, q_host, q_b)
@@ -346,15 +364,19 @@ def run_b200(args, w, rank, world):
         gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
         gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
         gpu.batch_commit(ctx)
-        gpu.gpu_buffer_2d_read(ctx, out_b, out_host)  # blocks until the result is on the host
+        if head_split and world > 1:
+            out_host_full.copy_(sharding.gather_heads(out_dev), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        else:
+            gpu.gpu_buffer_2d_read(ctx, out_b, out_host)  # blocks until the result is on the host
 
     for _ in range(3):
         step_e2e()
     ms_e2e = timed(step_e2e, steps) / steps
     clocks = sampler.finish()
-    e2e_tps = world * B / (ms_e2e * 1e-3)
+    e2e_tps = seqs_total / (ms_e2e * 1e-3)
     h2d = 3 * B * E * 2
-    d2h = B * E * 2
+    d2h = B * (H_total if head_split else H) * D * 2
 
     # ---- CPU baseline (rank 0, N=1 only) -----------------------------------------------
     cpu = None
@@ -378,13 +400,14 @@ def run_b200(args, w, rank, world):
         "warmup": warm,
         "ms_per_step": ms_step,
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong" if head_split else "weak",
         "vs_baseline": None,
         "dtype": "bf16 storage, fp32 arithmetic",
         "data": "synthetic",
-        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
-                   "sum_len_rank0": int(np.sum(lens0)), "l2": "inputs (9 GB cache) far larger than L2, no flush",
-                   "parallelism": f"batch-sharded x{world}, no collective in the step"},
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": seqs_total,
+                   "sum_len_rank0": int(np.sum(lens0)), "l2": "inputs (GBs of cache) far larger than L2, no flush",
+                   "parallelism": (f"heads split x{world}, one all-gather of the outputs per step" if head_split
+                                   else f"batch-sharded x{world}, no collective in the step")},
         "e2e": {"value": e2e_tps, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": 3 * steps,
@@ -395,6 +418,129 @@ def run_b200(args, w, rank, world):
                      "algorithmic_bytes_per_launch": dec_bytes,
                      "traffic": int(DRAM_BYTES_PER_TOKEN_HEAD * float(np.sum(lens0 + 1)) * H) if not bs else None},
         "step_hbm_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def measured_tensor_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return float(d["bf16_tflops_sustained"]), float(d["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1400.0, 1590.0, "fallback"
+
+
+def run_prefill(args, w, rank, world):
+    """Causal prefill fused with the cache write; value = prompt tokens/s, roofline = tensor."""
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pkg = __graft_entry__.import_package()
+    gpu = pkg.gpu
+    ctx = gpu.context_create(local_rank)
+    B, H, D, N = w["B"], w["H"], w["D"], w["N"]
+    E = H * D
+    dtype = torch.bfloat16
+    gen = torch.Generator(device=device).manual_seed(2000 + rank)
+    mk = lambda: torch.randn((B * N, E), generator=gen, device=device, dtype=torch.float32).to(dtype)  # noqa: E731
+    Q, K, V = mk(), mk(), mk()
+    O = torch.empty_like(Q)
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=N, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=dtype, layout="bhtd"))
+    wrap = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    Qb, Kb, Vb, Ob = wrap(Q), wrap(K), wrap(V), wrap(O)
+
+    def step_device():
+        gpu.batch_begin(ctx)
+        gpu.flash_attention(ctx, Qb, Kb, Vb, Ob, None, None, B, N, H, D, cache=cache, layer_idx=0)
+        gpu.batch_commit(ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    steps, warm = min(args.steps, 50), max(3, args.warmup)
+    for _ in range(warm):
+        step_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ms_step = timed(step_device, steps) / steps
+    Qh, Kh, Vh = Q.cpu().pin_memory(), K.cpu().pin_memory(), V.cpu().pin_memory()
+    Oh = torch.empty_like(Qh).pin_memory()
+
+    def step_e2e():
+        gpu.gpu_buffer_2d_write(ctx, Qh, Qb)
+        gpu.gpu_buffer_2d_write(ctx, Kh, Kb)
+        gpu.gpu_buffer_2d_write(ctx, Vh, Vb)
+        step_device()
+        gpu.gpu_buffer_2d_read(ctx, Ob, Oh)
+
+    step_e2e()
+    e2e_steps = max(2, min(steps, 5))
+    ms_e2e = timed(step_e2e, e2e_steps) / e2e_steps
+    clocks = sampler.finish()
+    flops = 4.0 * B * H * D * N * (N + 1) / 2
+    sustained, burst, kind = measured_tensor_peak()
+    achieved = flops / (ms_step * 1e-3) / 1e12
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import c_oracle
+
+        hs = 4  # heads of one sequence timed on the CPU
+        sl = lambda X: np.ascontiguousarray(  # noqa: E731
+            X.reshape(B, N, H, D)[0, :, :hs, :].reshape(N, hs * D).cpu().view(torch.int16).numpy().view(np.uint16))
+        t0 = time.perf_counter()
+        c_oracle.prefill(sl(Q), sl(K), sl(V), 1, N, hs, D, want_stats=False)
+        dt = time.perf_counter() - t0
+        cpu = {"value": N * hs / H / dt, "unit": "tokens/s", "cores": c_oracle.num_threads(), "kind": "port",
+               "sample": f"{hs} of {H} heads of one sequence ({dt:.2f} s); value counts {hs}/{H} of a token per row"}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "prefill tokens/s", "value": world * B * N / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
+                   "l2": "Q/K/V/O/cache (1.6 GB per step) larger than L2, no flush",
+                   "parallelism": f"batch-sharded x{world}, no collective"},
+        "e2e": {"value": world * B * N / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": 3 * B * N * E * 2, "d2h_bytes_per_step": B * N * E * 2},
+        "gpu_launches": steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": achieved, "peak": sustained,
+                     "unit": "TFLOP/s", "frac": achieved / sustained, "frac_of_burst": achieved / burst,
+                     "peak_kind": kind + " (sustained cuBLAS bf16; kernel timed in a loop)",
+                     "algorithmic_flops_per_launch": flops, "traffic": None},
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
@@ -419,6 +565,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     w = WORKLOADS[args.workload]
+    w.setdefault("block_size", 0)
+    if w.get("prefill") and args.impl != "reference":
+        run_prefill(args, w, rank, world)
+        return
     if args.impl == "reference":
         run_reference(args, w, rank)
         return

@@ -591,9 +591,13 @@ extern "C" {
 size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype) {
     const int es = elt_bytes(dtype);
     if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0 || es == 0 || (D * es) % 16 != 0) return 0;
-    // sized for the smallest split any variant may choose (one tile of the smallest tile size)
-    const size_t tile = static_cast<size_t>(smallest_tile(D * es));
-    const size_t c_max = (static_cast<size_t>(T_upper) + tile - 1) / tile;
+    // An upper bound of what any compiled variant will ask for: the split is chosen as the launch
+    // chooses it, but for the smallest tile of that row size and for a grid larger than any
+    // variant's (16 CTAs per SM), both of which can only make the split finer.
+    const int row = D * es;
+    const int tile = smallest_tile(row);
+    const int chunk = pick_chunk(B, H, T_upper, tile, row, device_sm_count() * 16);
+    const size_t c_max = (static_cast<size_t>(T_upper) + chunk - 1) / chunk;
     const size_t slots = static_cast<size_t>(B) * H * c_max;
     return align_up(slots * D * sizeof(float), 256) + slots * 2 * sizeof(float) + 256;
 }

@@ -152,9 +152,11 @@ def kv_cache_update(ctx: GPUContext, cache: KVCache, layer_idx: int, new_k: GPUB
 
 
 def decode_workspace(cache: KVCache) -> torch.Tensor:
-    if cache.workspace is None:
-        nbytes = _native.lib.b2kv_decode_workspace_bytes(cache.batch_size, cache.n_heads, cache.head_dim,
-                                                         cache.max_seq_len, dtype_code(cache.dtype))
+    """Scratch for the split-K partials, sized by the library for this cache's largest length;
+    allocated on first use and grown if a tuning knob later asks for a finer split."""
+    nbytes = _native.lib.b2kv_decode_workspace_bytes(cache.batch_size, cache.n_heads, cache.head_dim,
+                                                     cache.max_seq_len, dtype_code(cache.dtype))
+    if cache.workspace is None or cache.workspace.numel() < nbytes:
         cache.workspace = torch.empty(nbytes, dtype=torch.uint8, device=cache.layers[0].k_cache.buffer.device)
     return cache.workspace
 
