@@ -51,6 +51,8 @@ WORKLOADS = {
     "longctx_headsplit": dict(B=4, H=64, D=128, lo=131072, hi=131072, block_size=0, head_split=True,
                               desc="long-context decode: B=4 H=64 D=128 bf16, len 131072, heads split over the "
                                    "GPUs, outputs all-gathered with NCCL"),
+    "prefill_small": dict(B=2, H=32, D=128, N=4096, prefill=True,
+                          desc="causal prefill cut to 2 sequences (for profiler captures)"),
     "prefill": dict(B=8, H=32, D=128, N=4096, prefill=True,
                     desc="causal prefill: B=8 H=32 D=128 N=4096 bf16, fused with the K/V cache write"),
 }

@@ -4,21 +4,23 @@
 // online softmax with scalar fp32 dot products from workgroup memory.  Here QK^T and PV are
 // tcgen05.mma contractions with fp32 accumulators in tensor memory (TMEM):
 //
-//   * one CTA per (sequence, head, block of 128 query rows); 128-key K/V tiles up to the diagonal;
-//   * warp 4 issues TMA tiled loads (cp.async.bulk.tensor, 128-byte swizzle) of Q, K and V tiles
-//     into shared memory rings that complete on mbarriers;
-//   * warp 5 issues the MMAs from one thread: S = Q K^T (both operands K-major in shared memory)
-//     into one of two S buffers in TMEM, and O += P V with P read from TMEM (it overwrites the S
-//     buffer it was computed from) and V as an MN-major shared-memory operand.  QK^T of the next
-//     tile is issued before PV of the current one, so the tensor pipe works while the softmax runs;
-//   * warps 0-3 do the softmax: thread i owns query row i (= TMEM lane i), reads its S row with
-//     tcgen05.ld, keeps the running max / sum in registers in the log2 domain, writes P as packed
-//     bf16 with tcgen05.st.  O stays in TMEM for the whole row block and is rescaled only when a
-//     row's running max has grown by more than 2^8 since the last rescale (the factor cancels in
-//     O / l, so the result is the same);
-//   * epilogue: O / max(l, 1e-8) -> bf16, L and M as the reference writes them (:762-768), and the
-//     block's own K / V rows copied into the KV cache when one is given.
+//   * one CTA per (sequence, head, block of 256 query rows) = two 128-row tiles A and B that share
+//     every K/V tile; 128-key K/V tiles up to the diagonal (A stops one tile before B);
+//   * warp 8 issues TMA tiled loads (cp.async.bulk.tensor, 128-byte swizzle) of Q, K and V tiles
+//     into shared memory rings that complete on mbarriers, and at the end TMA-stores the two
+//     diagonal K / V tiles (the CTA's own rows) from the ring into the KV cache;
+//   * warp 9 issues the MMAs from one thread: S_X = Q_X K^T (both operands K-major in shared memory)
+//     into the S buffer of tile X in TMEM, and O_X += P_X V with P_X read from TMEM (it overwrites
+//     S_X) and V as an MN-major shared-memory operand.  The order PV_A(j), QK_A(j+1), PV_B(j),
+//     QK_B(j+1) keeps the tensor pipe busy with one tile while the other tile's softmax runs;
+//   * warps 0-3 (tile A) and 4-7 (tile B) do the softmax: thread i owns query row i (= TMEM lane i),
+//     reads its 128 scores with tcgen05.ld, keeps the running max / sum in registers in the log2
+//     domain and writes P as packed bf16 with tcgen05.st.  O stays in TMEM for the whole row block
+//     and is rescaled only when a row's running max has grown by more than 2^8 since the last
+//     rescale (the factor cancels in O / l, so the result is the same);
+//   * epilogue: O / max(l, 1e-8) -> bf16, L and M as the reference writes them (:762-768).
 //
+// TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511 (all 512).
 // Every mbarrier wait is bounded; a wait that runs out makes all warps fall through to the
 // common exit, where the tensor memory is released.
 #include <cuda.h>
@@ -30,26 +32,25 @@ namespace b2kv {
 
 namespace tc {
 
-constexpr int kBlockM = 128;  // query rows per CTA
-constexpr int kBlockN = 128;  // keys per tile
+constexpr int kTileM = 128;   // query rows per tile (two tiles per CTA)
+constexpr int kBlockN = 128;  // keys per K/V tile
 constexpr int kD = 128;
-constexpr int kKStages = 2, kVStages = 2;
-constexpr int kHalfTileBytes = 128 * 128;          // 128 rows x 64 bf16 (one 128-byte swizzle span per row)
-constexpr int kTileBytes = 2 * kHalfTileBytes;     // 128 x 128 bf16
-constexpr int kThreads = 192;
+constexpr int kStages = 2;                      // K ring and V ring depth
+constexpr int kHalfTileBytes = 128 * 128;       // 128 rows x 64 bf16 (one 128-byte swizzle span per row)
+constexpr int kTileBytes = 2 * kHalfTileBytes;  // 128 x 128 bf16
+constexpr int kThreads = 320;
 constexpr int kTmemCols = 512;
-constexpr int kColS0 = 0, kColS1 = 128, kColO = 256;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kColS = 0, kColO = 256;       // + 128 for tile B
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
 struct SharedStorage {
-    alignas(1024) uint8_t q[kTileBytes];
-    alignas(1024) uint8_t k[kKStages][kTileBytes];
-    alignas(1024) uint8_t v[kVStages][kTileBytes];
+    alignas(1024) uint8_t q[2][kTileBytes];
+    alignas(1024) uint8_t k[kStages][kTileBytes];
+    alignas(1024) uint8_t v[kStages][kTileBytes];
     alignas(8) uint64_t q_full;
-    uint64_t k_full[kKStages], k_empty[kKStages];
-    uint64_t v_full[kVStages], v_empty[kVStages];
-    uint64_t s_full[2], p_ready[2];
-    uint64_t o_done;
+    uint64_t k_full[kStages], k_empty[kStages];
+    uint64_t v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2], p_ready[2], o_done[2];  // per query tile
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -165,41 +166,63 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Shared -> global tiled store (TMA); completion is tracked with bulk groups of the issuing thread.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the committed stores have completed.
+__device__ __forceinline__ void tma_store_wait() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// 128 consecutive fp32 columns of this thread's TMEM lane, as four 32-column loads in flight together.
+__device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t(&q)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]);
+        tmem_ld32(taddr + c * 32, q);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
+                  const __grid_constant__ CUtensorMap tm_vc, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     SharedStorage& sm =
         *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_qb = (p.N + kBlockM - 1) / kBlockM;
-    // heaviest query blocks (most K/V tiles) first
-    const int qb = n_qb - 1 - static_cast<int>(blockIdx.x / (p.H * p.B));
+    const int n_cb = (p.N + 2 * kTileM - 1) / (2 * kTileM);
+    // heaviest row blocks (most K/V tiles) first
+    const int cb = n_cb - 1 - static_cast<int>(blockIdx.x / (p.H * p.B));
     const int bh = blockIdx.x % (p.H * p.B);
     const int b = bh / p.H, h = bh % p.H;
-    const int q0 = qb * kBlockM;
-    const int n_tiles = qb + 1;  // causal: K/V tiles 0 .. qb
+    const int q0 = cb * 2 * kTileM;
+    const int qa = 2 * cb;                                 // K/V tile index of tile A's diagonal
+    const int n_a = qa + 1;                                // tile A attends K/V tiles 0 .. qa
+    const int n_b = (q0 + kTileM < p.N) ? qa + 2 : 0;      // tile B attends 0 .. qa + 1 (absent past the end)
+    const int n_max = n_b > n_a ? n_b : n_a;
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        for (int s = 0; s < kKStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(&sm.k_full[s], 1);
             mbar_init(&sm.k_empty[s], 1);
-        }
-        for (int s = 0; s < kVStages; ++s) {
             mbar_init(&sm.v_full[s], 1);
             mbar_init(&sm.v_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&sm.s_full[s], 1);
-            mbar_init(&sm.p_ready[s], 128);
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(&sm.s_full[x], 1);
+            mbar_init(&sm.p_ready[x], 128);
+            mbar_init(&sm.o_done[x], 1);
         }
-        mbar_init(&sm.o_done, 1);
         sm.abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(&sm.tmem_base, kTmemCols);
         tmem_relinquish();
     }
@@ -208,60 +231,65 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             const int x0 = h * kD;
-            mbar_arrive_expect_tx(&sm.q_full, kTileBytes);
-            tma_load_3d(sm.q, &tm_q, &sm.q_full, x0, q0, b);
-            tma_load_3d(sm.q + kHalfTileBytes, &tm_q, &sm.q_full, x0 + 64, q0, b);
-            for (int j = 0; j < n_tiles && !sm.abort_flag; ++j) {
-                const int ks = j % kKStages, vs = j % kVStages;
-                if (!mbar_wait(&sm.k_empty[ks], ((j / kKStages) & 1) ^ 1)) {
-                    sm.abort_flag = 1;
-                    break;
-                }
-                mbar_arrive_expect_tx(&sm.k_full[ks], kTileBytes);
-                tma_load_3d(sm.k[ks], &tm_k, &sm.k_full[ks], x0, j * kBlockN, b);
-                tma_load_3d(sm.k[ks] + kHalfTileBytes, &tm_k, &sm.k_full[ks], x0 + 64, j * kBlockN, b);
-                if (!mbar_wait(&sm.v_empty[vs], ((j / kVStages) & 1) ^ 1)) {
-                    sm.abort_flag = 1;
-                    break;
-                }
-                mbar_arrive_expect_tx(&sm.v_full[vs], kTileBytes);
-                tma_load_3d(sm.v[vs], &tm_v, &sm.v_full[vs], x0, j * kBlockN, b);
-                tma_load_3d(sm.v[vs] + kHalfTileBytes, &tm_v, &sm.v_full[vs], x0 + 64, j * kBlockN, b);
+            mbar_arrive_expect_tx(&sm.q_full, (n_b > 0 ? 2 : 1) * kTileBytes);
+            tma_load_3d(sm.q[0], &tm_q, &sm.q_full, x0, q0, b);
+            tma_load_3d(sm.q[0] + kHalfTileBytes, &tm_q, &sm.q_full, x0 + 64, q0, b);
+            if (n_b > 0) {
+                tma_load_3d(sm.q[1], &tm_q, &sm.q_full, x0, q0 + kTileM, b);
+                tma_load_3d(sm.q[1] + kHalfTileBytes, &tm_q, &sm.q_full, x0 + 64, q0 + kTileM, b);
             }
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int st = j % kStages;
+                const uint32_t par = ((j / kStages) & 1) ^ 1;
+                ok = mbar_wait(&sm.k_empty[st], par);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+                tma_load_3d(sm.k[st], &tm_k, &sm.k_full[st], x0, j * kBlockN, b);
+                tma_load_3d(sm.k[st] + kHalfTileBytes, &tm_k, &sm.k_full[st], x0 + 64, j * kBlockN, b);
+                ok = mbar_wait(&sm.v_empty[st], par);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+                tma_load_3d(sm.v[st], &tm_v, &sm.v_full[st], x0, j * kBlockN, b);
+                tma_load_3d(sm.v[st] + kHalfTileBytes, &tm_v, &sm.v_full[st], x0 + 64, j * kBlockN, b);
+            }
+            // The CTA's own K / V rows are the last one (A only) or two K/V tiles; they are still in
+            // the rings.  Once the MMAs that read a tile have completed (its "empty" barrier), store
+            // it to the cache.  Rows past the sequence end are clipped by the tensor map.
+            if (ok && p.k_cache != nullptr) {
+                for (int t = qa; t < n_max && ok; ++t) {
+                    const int st = t % kStages;
+                    ok = mbar_wait(&sm.k_empty[st], (t / kStages) & 1);
+                    if (!ok) break;
+                    tma_store_4d(&tm_kc, sm.k[st], 0, t * kBlockN, h, b);
+                    tma_store_4d(&tm_kc, sm.k[st] + kHalfTileBytes, 64, t * kBlockN, h, b);
+                }
+                for (int t = qa; t < n_max && ok; ++t) {
+                    const int st = t % kStages;
+                    ok = mbar_wait(&sm.v_empty[st], (t / kStages) & 1);
+                    if (!ok) break;
+                    tma_store_4d(&tm_vc, sm.v[st], 0, t * kBlockN, h, b);
+                    tma_store_4d(&tm_vc, sm.v[st] + kHalfTileBytes, 64, t * kBlockN, h, b);
+                }
+                tma_store_commit();
+                tma_store_wait();
+            }
+            if (!ok) sm.abort_flag = 1;
         }
         __syncwarp();
-        // the block's own K / V rows -> cache (bit-exact copy), overlapped with the compute
-        if (p.k_cache != nullptr) {
-            const int E = p.H * kD;
-            const __nv_bfloat16* Kg = static_cast<const __nv_bfloat16*>(p.K) + static_cast<size_t>(b) * p.N * E + h * kD;
-            const __nv_bfloat16* Vg = static_cast<const __nv_bfloat16*>(p.V) + static_cast<size_t>(b) * p.N * E + h * kD;
-            __nv_bfloat16* kc = static_cast<__nv_bfloat16*>(p.k_cache);
-            __nv_bfloat16* vc = static_cast<__nv_bfloat16*>(p.v_cache);
-            const int rows = min(kBlockM, p.N - q0);
-            for (int i = lane; i < rows * 16; i += 32) {
-                const int r = i >> 4, c = i & 15;
-                const size_t src = static_cast<size_t>(q0 + r) * E + c * 8;
-                const int64_t dst = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(q0 + r) * p.stride_t +
-                                    static_cast<int64_t>(h) * p.stride_h + c * 8;
-                *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(Kg + src);
-                *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(Vg + src);
-            }
-        }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(0, 0);
             constexpr uint32_t idesc_pv = instr_desc(0, 1);
-            const uint32_t q_addr = smem_u32(sm.q);
-            bool ok = mbar_wait(&sm.q_full, 0);
-            auto issue_qk = [&](int j) {
-                const int ks = j % kKStages;
-                const uint32_t k_addr = smem_u32(sm.k[ks]);
-                const uint32_t s_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+            auto issue_qk = [&](int x, int j) {
+                const uint32_t q_addr = smem_u32(sm.q[x]);
+                const uint32_t k_addr = smem_u32(sm.k[j % kStages]);
+                const uint32_t s_tmem = tmem + kColS + x * 128;
 #pragma unroll
                 for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
@@ -271,67 +299,92 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                (kb | kk) ? 1u : 0u);
                     }
                 }
-                mma_commit(&sm.s_full[j & 1]);
-                mma_commit(&sm.k_empty[ks]);
+                mma_commit(&sm.s_full[x]);
             };
-            if (ok) ok = mbar_wait(&sm.k_full[0], 0);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-            }
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) {
-                    ok = mbar_wait(&sm.k_full[(j + 1) % kKStages], ((j + 1) / kKStages) & 1);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(j + 1);
-                }
-                const int vs = j % kVStages;
-                ok = mbar_wait(&sm.p_ready[j & 1], (j >> 1) & 1) && mbar_wait(&sm.v_full[vs], (j / kVStages) & 1);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(sm.v[vs]);
-                const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+            auto issue_pv = [&](int x, int j) {
+                const uint32_t v_addr = smem_u32(sm.v[j % kStages]);
+                const uint32_t p_tmem = tmem + kColS + x * 128;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     // 16 keys per step: 8 packed columns of P, 16 rows (2048 bytes) of V
-                    mma_ts(tmem + kColO, p_tmem + kk * 8, smem_desc(v_addr + kk * 2048, kHalfTileBytes, 1024), idesc_pv,
-                           (j | kk) ? 1u : 0u);
+                    mma_ts(tmem + kColO + x * 128, p_tmem + kk * 8,
+                           smem_desc(v_addr + kk * 2048, kHalfTileBytes, 1024), idesc_pv, (j | kk) ? 1u : 0u);
                 }
-                mma_commit(&sm.v_empty[vs]);
-                mma_commit(&sm.o_done);
+                mma_commit(&sm.o_done[x]);
+            };
+            bool ok = mbar_wait(&sm.q_full, 0) && mbar_wait(&sm.k_full[0], 0);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0, 0);
+                if (n_b > 0) issue_qk(1, 0);
+                mma_commit(&sm.k_empty[0]);
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int st = j % kStages;
+                const uint32_t par = (j / kStages) & 1;
+                const int st1 = (j + 1) % kStages;
+                const uint32_t par1 = ((j + 1) / kStages) & 1;
+                if (j < n_a) {
+                    ok = mbar_wait(&sm.p_ready[0], j & 1) && mbar_wait(&sm.v_full[st], par);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(0, j);
+                }
+                if (j + 1 < n_a) {
+                    ok = mbar_wait(&sm.k_full[st1], par1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(0, j + 1);
+                }
+                if (j < n_b) {
+                    ok = mbar_wait(&sm.p_ready[1], j & 1) && mbar_wait(&sm.v_full[st], par);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(1, j);
+                }
+                mma_commit(&sm.v_empty[st]);
+                if (j + 1 < n_b) {
+                    ok = mbar_wait(&sm.k_full[st1], par1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(1, j + 1);
+                }
+                if (j + 1 < n_max) mma_commit(&sm.k_empty[st1]);
             }
             if (!ok) sm.abort_flag = 1;
         }
         __syncwarp();
     } else {
         // ------------------------------ softmax: thread = query row ------------------------------
-        const int row = threadIdx.x;  // 0..127, also the TMEM lane
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const int x = warp >> 2;             // 0 = tile A, 1 = tile B
+        const int row = threadIdx.x & 127;   // row inside the tile, also the TMEM lane
+        const int n_x = x ? n_b : n_a;
+        const int diag_tile = qa + x;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_base + kColS + x * 128;
+        const uint32_t o_tmem = tmem + lane_base + kColO + x * 128;
         const float c = p.q_prescale;  // log2(e) / sqrt(D)
         float m_used = -INFINITY, m_run = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const uint32_t s_tmem = tmem + lane_base + ((j & 1) ? kColS1 : kColS0);
-            ok = mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1);
+        for (int j = 0; j < n_x && ok; ++j) {
+            ok = mbar_wait(&sm.s_full[x], j & 1);
             if (!ok) break;
             tc_fence_after();
-            const bool diag = (j == qb);
-            // pass 1: row maximum of the raw scores
+            uint32_t r[128];
+            tmem_ld128(s_tmem, r);
+            tmem_wait_ld();
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(s_tmem + cc * 32, r);
-                tmem_wait_ld();
+            if (j == diag_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float s = __uint_as_float(r[i]);
-                    if (!diag || (cc * 32 + i) <= row) mx = fmaxf(mx, s);
+                for (int i = 0; i < 128; ++i) {
+                    if (i > row) r[i] = 0xff800000u;  // -inf: key after the query
+                    mx = fmaxf(mx, __uint_as_float(r[i]));
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
             }
-            const float mx_scaled = mx * c;
-            m_run = fmaxf(m_run, mx_scaled);
+            m_run = fmaxf(m_run, mx * c);
             float factor = 1.f;
             bool need = false;
             if (j == 0) {
@@ -341,70 +394,64 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 m_used = m_run;
                 need = true;
             }
-            // pass 2: P = exp2(s*c - m_used) as packed bf16 over the first 64 columns of the S buffer
-            float sum = 0.f;
-#pragma unroll 1
+            // P = exp2(s*c - m_used) as packed bf16 over the first 64 columns of the S buffer
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(s_tmem + cc * 32, r);
-                tmem_wait_ld();
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), c, -m_used));
-                    float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), c, -m_used));
-                    if (diag) {
-                        if (cc * 32 + 2 * i > row) p0 = 0.f;
-                        if (cc * 32 + 2 * i + 1 > row) p1 = 0.f;
-                    }
-                    sum += p0 + p1;
+                    const float p0 = exp2f(fmaf(__uint_as_float(r[cc * 32 + 2 * i]), c, -m_used));
+                    const float p1 = exp2f(fmaf(__uint_as_float(r[cc * 32 + 2 * i + 1]), c, -m_used));
+                    sum0 += p0;
+                    sum1 += p1;
                     pk[i] = pack_bf16(p0, p1);
                 }
                 tmem_st16(s_tmem + cc * 16, pk);
             }
-            l = l * factor + sum;
+            l = l * factor + (sum0 + sum1);
             // rare: bring O down to the new reference maximum (needs PV of the previous tile finished)
             if (__any_sync(0xffffffffu, need)) {
-                ok = mbar_wait(&sm.o_done, (j - 1) & 1);
+                ok = mbar_wait(&sm.o_done[x], (j - 1) & 1);
                 if (ok) {
                     tc_fence_after();
 #pragma unroll 1
                     for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem + lane_base + kColO + cc * 32, r);
+                        uint32_t o[32];
+                        tmem_ld32(o_tmem + cc * 32, o);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-                        tmem_st32(tmem + lane_base + kColO + cc * 32, r);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                        tmem_st32(o_tmem + cc * 32, o);
                     }
                 }
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sm.p_ready[j & 1]);
+            mbar_arrive(&sm.p_ready[x]);
         }
-        if (ok) ok = mbar_wait(&sm.o_done, (n_tiles - 1) & 1);
-        if (ok) {
+        if (ok && n_x > 0) ok = mbar_wait(&sm.o_done[x], (n_x - 1) & 1);
+        if (ok && n_x > 0) {
             tc_fence_after();
-            const int grow = q0 + row;
+            const int grow = q0 + x * kTileM + row;
             const float inv = 1.f / fmaxf(l, 1e-8f);
             const int E = p.H * kD;
             __nv_bfloat16* Og =
                 static_cast<__nv_bfloat16*>(p.O) + (static_cast<size_t>(b) * p.N + grow) * E + static_cast<size_t>(h) * kD;
 #pragma unroll 1
             for (int cc = 0; cc < 4; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + kColO + cc * 32, r);
+                uint32_t o[32];
+                tmem_ld32(o_tmem + cc * 32, o);
                 tmem_wait_ld();
                 if (grow < p.N) {
 #pragma unroll
                     for (int v4 = 0; v4 < 4; ++v4) {
-                        uint4 o;
-                        o.x = pack_bf16(__uint_as_float(r[v4 * 8 + 0]) * inv, __uint_as_float(r[v4 * 8 + 1]) * inv);
-                        o.y = pack_bf16(__uint_as_float(r[v4 * 8 + 2]) * inv, __uint_as_float(r[v4 * 8 + 3]) * inv);
-                        o.z = pack_bf16(__uint_as_float(r[v4 * 8 + 4]) * inv, __uint_as_float(r[v4 * 8 + 5]) * inv);
-                        o.w = pack_bf16(__uint_as_float(r[v4 * 8 + 6]) * inv, __uint_as_float(r[v4 * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(Og + cc * 32 + v4 * 8) = o;
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(Og + cc * 32 + v4 * 8) = w;
                     }
                 }
             }
@@ -413,7 +460,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (p.L) p.L[sidx] = l * exp2f(m_used - m_run);
                 if (p.M) p.M[sidx] = m_run * 0.6931471805599453f;
             }
-        } else {
+        } else if (!ok) {
             sm.abort_flag = 1;
         }
     }
@@ -421,7 +468,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // common exit: every warp arrives here, then the allocating warp releases the tensor memory
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
@@ -457,18 +504,44 @@ static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E) {
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// View of a cache of any layout as (d, token, head, sequence), cut to the first N tokens so that a
+// store of a partly filled tile leaves the rows past the sequence end untouched.
+static bool make_cache_map(CUtensorMap* map, void* base, int B, int N, int H, int64_t sb, int64_t st, int64_t sh) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(H),
+                                static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
+                                   static_cast<cuuint64_t>(sb) * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+           CUDA_SUCCESS;
+}
+
 }  // namespace tc
 
 int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) {
     if (dtype != B2KV_DTYPE_BF16 || D != tc::kD) return B2KV_ERR_UNSUPPORTED;
     const int E = p.H * D;
-    const long long n_qb = (p.N + tc::kBlockM - 1) / tc::kBlockM;
-    const long long ctas = n_qb * p.H * p.B;
+    const long long n_cb = (p.N + 2 * tc::kTileM - 1) / (2 * tc::kTileM);
+    const long long ctas = n_cb * p.H * p.B;
     if (ctas > 0x7fffffffLL) return B2KV_ERR_UNSUPPORTED;
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, tkc, tvc;
     if (!tc::make_map(&tq, p.Q, p.B, p.N, E) || !tc::make_map(&tk, p.K, p.B, p.N, E) ||
         !tc::make_map(&tv, p.V, p.B, p.N, E))
         return B2KV_ERR_UNSUPPORTED;  // no tensor-map encoder in this driver: the SIMT kernel takes over
+    if (p.k_cache != nullptr) {
+        // a cache whose strides a tensor map cannot express goes to the SIMT kernel
+        if (p.stride_t < D || p.stride_h <= 0 || p.stride_b <= 0) return B2KV_ERR_UNSUPPORTED;
+        if (!tc::make_cache_map(&tkc, p.k_cache, p.B, p.N, p.H, p.stride_b, p.stride_t, p.stride_h) ||
+            !tc::make_cache_map(&tvc, p.v_cache, p.B, p.N, p.H, p.stride_b, p.stride_t, p.stride_h))
+            return B2KV_ERR_UNSUPPORTED;
+    } else {
+        tkc = tk;  // never dereferenced when no cache is given
+        tvc = tv;
+    }
     constexpr size_t smem = sizeof(tc::SharedStorage) + 1024;
     static bool configured[64] = {false};
     int dev = 0;
@@ -479,8 +552,8 @@ int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) 
                                            static_cast<int>(smem)));
         configured[dev] = true;
     }
-    tc::prefill_tc_kernel<<<static_cast<unsigned>(ctas), tc::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv,
-                                                                                                                  p);
+    tc::prefill_tc_kernel<<<static_cast<unsigned>(ctas), tc::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        tq, tk, tv, tkc, tvc, p);
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
 }
