@@ -161,6 +161,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+// 2^x on the special-function unit (one MUFU.EX2; exp2f would add range handling around it).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);  // .x = lo (low 16 bits), .y = hi
     return *reinterpret_cast<uint32_t*>(&v);
@@ -373,42 +380,50 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             uint32_t r[128];
             tmem_ld128(s_tmem, r);
             tmem_wait_ld();
-            float mx = -INFINITY;
+            // row maximum with eight independent chains (a single chain of 128 dependent max
+            // operations would cost more than the exponentials)
             if (j == diag_tile) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
+                for (int i = 0; i < 128; ++i)
                     if (i > row) r[i] = 0xff800000u;  // -inf: key after the query
-                    mx = fmaxf(mx, __uint_as_float(r[i]));
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
             }
+            float mxs[8];
+#pragma unroll
+            for (int a = 0; a < 8; ++a) mxs[a] = __uint_as_float(r[a]);
+#pragma unroll
+            for (int i = 8; i < 128; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(r[i]));
+            const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                                   fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
             m_run = fmaxf(m_run, mx * c);
             float factor = 1.f;
             bool need = false;
             if (j == 0) {
                 m_used = m_run;
             } else if (m_run > m_used + kRescaleThreshold) {
-                factor = exp2f(m_used - m_run);
+                factor = ex2(m_used - m_run);
                 m_used = m_run;
                 need = true;
             }
             // P = exp2(s*c - m_used) as packed bf16 over the first 64 columns of the S buffer
-            float sum0 = 0.f, sum1 = 0.f;
+            float sums[8];
+#pragma unroll
+            for (int a = 0; a < 8; ++a) sums[a] = 0.f;
+            const float neg_m = -m_used;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = exp2f(fmaf(__uint_as_float(r[cc * 32 + 2 * i]), c, -m_used));
-                    const float p1 = exp2f(fmaf(__uint_as_float(r[cc * 32 + 2 * i + 1]), c, -m_used));
-                    sum0 += p0;
-                    sum1 += p1;
+                    const float p0 = ex2(fmaf(__uint_as_float(r[cc * 32 + 2 * i]), c, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(r[cc * 32 + 2 * i + 1]), c, neg_m));
+                    sums[(2 * i) & 7] += p0;
+                    sums[(2 * i + 1) & 7] += p1;
                     pk[i] = pack_bf16(p0, p1);
                 }
                 tmem_st16(s_tmem + cc * 16, pk);
             }
+            const float sum0 = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            const float sum1 = (sums[4] + sums[5]) + (sums[6] + sums[7]);
             l = l * factor + (sum0 + sum1);
             // rare: bring O down to the new reference maximum (needs PV of the previous tile finished)
             if (__any_sync(0xffffffffu, need)) {
@@ -457,7 +472,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             if (grow < p.N) {
                 const size_t sidx = (static_cast<size_t>(b) * p.N + grow) * p.H + h;
-                if (p.L) p.L[sidx] = l * exp2f(m_used - m_run);
+                if (p.L) p.L[sidx] = l * ex2(m_used - m_run);
                 if (p.M) p.M[sidx] = m_run * 0.6931471805599453f;
             }
         } else if (!ok) {
