@@ -173,6 +173,8 @@ def cpu_port_run(w, lens, steps, warmup, sample_seqs, log=None):
     nk = kv_oracle.f32_to_bf16_bits(rng.standard_normal((Bs, H * D)).astype(np.float32))
     nv = kv_oracle.f32_to_bf16_bits(rng.standard_normal((Bs, H * D)).astype(np.float32))
     strides = (H * T_max * D, D, T_max * D)
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host core
+    c_oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count())
     threads = c_oracle.num_threads()
     pos = sl.copy()
 

@@ -108,7 +108,7 @@ int b2kv_gather_paged(const void* pool, void* out, const int32_t* seq_lens, int 
  * 256 cached tokens (gpu_kv_cache.py:250-257) does not exist here: the cache is
  * processed split-K (flash decoding) and the partial results are merged by a second
  * small kernel.  T_upper is a host-side upper bound of every n_b (at most T_max); it
- * sizes the workspace and the split.  len_bias lets a caller attend over "length after
+ * bounds the lengths read from the device and the size of the launch.  len_bias lets a caller attend over "length after
  * this step's append" without a separate increment of the device lengths.
  * `workspace` is scratch of at least b2kv_decode_workspace_bytes(...) bytes; it needs no
  * initialisation and carries nothing between calls.
@@ -137,10 +137,10 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
  * performs no cudaMalloc / cudaFree and calls no allocating routine.
  *
  * Limits and rules:
- *   - Shapes whose partials do not fit (B * H * ceil(T_upper / split) * (D + 2) * 4 bytes with the
- *     split the library chooses) are refused with B2KV_ERR_STATIC_LIMIT before anything is
- *     launched; use b2kv_decode with your own workspace for those.  The benchmark shape
- *     (B=64, H=32, D=128, T_upper <= 9216, bf16) needs about 10 MB.
+ *   - Shapes whose partials do not fit (B * H * (ceil(CTAs / H) + 2) slots of (D + 2) * 4 bytes,
+ *     CTAs = the persistent grid, two per SM for 256-byte rows) are refused with
+ *     B2KV_ERR_STATIC_LIMIT before anything is launched; use b2kv_decode with your own
+ *     workspace for those.  The benchmark shape (B=64, H=32, D=128, bf16) needs about 13 MB.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call before starting
  *     any stream capture on that device.
@@ -172,7 +172,7 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
 
 /*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
- * "decode_chunk", "decode_grid_per_sm", "prefill_force_simt"); returns B2KV_ERR_BAD_ARG
+ * "decode_grid_per_sm", "decode_l2_keep", "prefill_force_simt"); returns B2KV_ERR_BAD_ARG
  * for an unknown name.  Defaults are chosen per shape when a knob is 0.  No counterpart in
  * the reference beyond the tile-size fields of GPUConfig (gpu_types.py:69-121).
  */

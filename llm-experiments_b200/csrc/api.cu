@@ -23,8 +23,8 @@ struct Knob {
 
 static Knob g_knobs[] = {
     {"decode_variant", 0},      // which compiled (tile, stages, warps) variant of the split kernel
-    {"decode_chunk", 0},        // tokens per split; 0 = chosen from the shape
     {"decode_grid_per_sm", 0},  // resident CTAs per SM to launch; 0 = occupancy
+    {"decode_l2_keep", 0},  // 1 = K/V bulk copies use the default L2 policy instead of evict-first
     {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
     {"prefill_variant", 0},
 };

@@ -2,9 +2,12 @@
 //
 // The reference kernel (simple-llm/src/gpu/gpu_kernels.py:2801-2938) gives one workgroup
 // to each (sequence, head), keeps the whole score vector in workgroup memory (hence its
-// 256-token limit) and reads K rows uncoalesced.  Here the cache is cut into work items of
-// `chunk` tokens of one (sequence, head); a persistent grid of CTAs walks the items
-// round-robin.  Inside a CTA one producer warp streams K/V tiles from HBM into a ring of
+// 256-token limit) and reads K rows uncoalesced.  Here all (sequence, head) caches of the batch
+// are laid end to end in one token space of H * sum(n_b) tokens, which is cut into one equal
+// share per CTA of a persistent grid (cuts rounded to whole tiles inside a (sequence, head)), so
+// ragged batches stay balanced without any scheduling traffic.  A share may cover the tail of
+// one (sequence, head), several whole ones and the head of another; every piece is a work
+// item.  Inside a CTA one producer warp streams K/V tiles from HBM into a ring of
 // shared-memory stages with bulk copies (TMA, untiled) that complete on mbarriers, and the
 // consumer warps fold each tile into an online softmax held in registers.  The producer
 // runs ahead across item boundaries, so the copy queue never drains between items.  Each
@@ -44,9 +47,10 @@ struct DecodeParams {
     int32_t* dev_status;
     int len_scalar, len_bias;
     int B, H, T_upper;
-    int chunk, c_max;  // tokens per item, items per (b, h) at most
+    int max_seg;  // partial-result slots per (sequence, head): the most CTA shares one can overlap
     int max_blocks, block_size, n_blocks;
     int run_len;  // tokens that one bulk copy may cover (contiguous in memory)
+    int l2_evict_first;  // 1: K/V copies carry the evict-first L2 policy (each row is read once)
     int64_t stride_b, stride_t, stride_h;
     float q_prescale;
 };
@@ -80,6 +84,72 @@ struct DecodeCfg {
 };
 
 // --------------------------------------------------------------------------------------
+// work split: one contiguous share of the batch's token space per CTA
+// --------------------------------------------------------------------------------------
+
+struct Share {
+    long long start, end;  // this CTA's range of the token space [0, H * sum_b n_b)
+    long long size;        // tokens per share (a multiple of the tile, the same for every CTA)
+};
+
+// Every thread of the calling warp takes part (the lengths are summed across the lanes).
+__device__ __forceinline__ Share share_of(const DecodeParams& p, int cta, int n_ctas, int tile, int lane) {
+    long long sum = 0;
+    for (int b = lane; b < p.B; b += 32) sum += seq_len_of(p, b);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const long long total = sum * p.H;
+    long long size = (total + n_ctas - 1) / n_ctas;
+    size = (size + tile - 1) / tile * tile;
+    if (size < tile) size = tile;
+    Share s;
+    s.size = size;
+    s.start = min(static_cast<long long>(cta) * size, total);
+    s.end = min(s.start + size, total);
+    return s;
+}
+
+// The piece [t_begin, t_end) of a (sequence, head) of `len` tokens at `pair_off` in the token
+// space that the share [start, end) owns.  Cuts inside the pair are rounded up to whole tiles
+// (relative to the pair's first token); the neighbouring share rounds the same cut the same way.
+__device__ __forceinline__ void piece_of(long long start, long long end, long long pair_off, int len, int tile,
+                                         int& t_begin, int& t_end) {
+    long long lo = 0, hi = len;
+    if (pair_off < start) lo = (start - pair_off + tile - 1) / tile * tile;
+    if (pair_off + len > end) hi = (end - pair_off + tile - 1) / tile * tile;
+    if (hi > len) hi = len;
+    if (lo > hi) lo = hi;
+    t_begin = static_cast<int>(lo);
+    t_end = static_cast<int>(hi);
+}
+
+// Finds the sequence b whose tokens contain position `pos` of the token space, 32 sequences per
+// step (warp scan of the lengths).  Every thread of the calling warp takes part and gets the result.
+__device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long pos, int lane, int& b,
+                                                long long& tok_before, int& len_b) {
+    long long before = 0;
+    b = p.B;
+    for (int b0 = 0; b0 < p.B; b0 += 32) {
+        const int len = (b0 + lane < p.B) ? seq_len_of(p, b0 + lane) : 0;
+        long long incl = len;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const long long up = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += up;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, (before + incl) * p.H > pos);
+        if (hit != 0u) {
+            const int l0 = __ffs(hit) - 1;
+            b = b0 + l0;
+            tok_before = before + __shfl_sync(0xffffffffu, incl - len, l0);
+            len_b = __shfl_sync(0xffffffffu, len, l0);
+            return;
+        }
+        before += __shfl_sync(0xffffffffu, incl, 31);
+    }
+}
+
+// --------------------------------------------------------------------------------------
 // producer warp
 // --------------------------------------------------------------------------------------
 
@@ -94,27 +164,26 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, uint8_t* 
     long long fills = 0;  // stages filled so far (for the drain after a failed wait)
     bool ok = true;
 
-    int b = 0;
-    long long base = 0;  // items that precede sequence b
-    int len_b = seq_len_of(p, 0);
-    int nch_b = (len_b + p.chunk - 1) / p.chunk;
+    const uint64_t l2_policy = l2_policy_evict_first();
+    const Share sh = share_of(p, blockIdx.x, gridDim.x, TILE_T, lane);
+    // first (sequence, head) that the share touches
+    int b = p.B;
+    long long tok_before = 0;  // tokens of the sequences that precede b
+    int len_b = 0;
+    if (sh.start < sh.end) locate_sequence(p, sh.start, lane, b, tok_before, len_b);
+    int h = (b < p.B) ? static_cast<int>((sh.start - tok_before * p.H) / len_b) : 0;
 
-    for (long long w = blockIdx.x; ok; w += gridDim.x) {
-        while (b < p.B && w >= base + static_cast<long long>(p.H) * nch_b) {
-            base += static_cast<long long>(p.H) * nch_b;
-            ++b;
-            if (b < p.B) {
-                len_b = seq_len_of(p, b);
-                nch_b = (len_b + p.chunk - 1) / p.chunk;
-            }
+    while (ok && b < p.B) {
+        const long long pair_off = tok_before * p.H + static_cast<long long>(h) * len_b;
+        if (pair_off >= sh.end) break;
+        int t_begin, t_end;
+        piece_of(sh.start, sh.end, pair_off, len_b, TILE_T, t_begin, t_end);
+        const long long seg = static_cast<long long>(blockIdx.x) - pair_off / sh.size;
+        if (t_begin < t_end && (seg < 0 || seg >= p.max_seg)) {
+            report_status(p.dev_status, B2KV_DEV_BAD_POSITION);  // cannot happen: sized on the host
+            t_end = t_begin;
         }
-        if (b >= p.B) break;
-        const int local = static_cast<int>(w - base);
-        const int c = local / p.H;
-        const int h = local - c * p.H;
-        const int t_begin = c * p.chunk;
-        const int t_end = min(len_b, t_begin + p.chunk);
-        const int slot = (b * p.H + h) * p.c_max + c;
+        const int slot = (b * p.H + h) * p.max_seg + static_cast<int>(seg);
 
         for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
             const int ntok = min(TILE_T, t_end - t0);
@@ -159,14 +228,28 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, uint8_t* 
                 off = (off + static_cast<int64_t>(h) * p.stride_h) * static_cast<int64_t>(sizeof(T));
                 const uint32_t bytes = static_cast<uint32_t>(cnt) * Cfg::kRowBytes;
                 const int dst = (tok - t0) * Cfg::kRowBytes;
-                bulk_g2s(sbase + dst, kbase + off, bytes, &full[stage]);
-                bulk_g2s(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage]);
+                if (p.l2_evict_first) {
+                    bulk_g2s_hint(sbase + dst, kbase + off, bytes, &full[stage], l2_policy);
+                    bulk_g2s_hint(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage], l2_policy);
+                } else {
+                    bulk_g2s(sbase + dst, kbase + off, bytes, &full[stage]);
+                    bulk_g2s(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage]);
+                }
             }
             ++fills;
             if (++stage == STAGES) {
                 stage = 0;
                 phase ^= 1u;
             }
+        }
+        // next (sequence, head); empty sequences own no tokens and are skipped
+        if (++h == p.H) {
+            h = 0;
+            tok_before += len_b;
+            do {
+                ++b;
+                len_b = (b < p.B) ? seq_len_of(p, b) : 0;
+            } while (b < p.B && len_b == 0);
         }
     }
 
@@ -397,24 +480,55 @@ __global__ void __launch_bounds__((NCW + 1) * 32) decode_split_kernel(const Deco
     }
 }
 
-// One CTA per (sequence, head), one thread per output column.
+// One CTA per (sequence, head), one thread per output column.  Recomputes which shares of the
+// split kernel's grid (`n_ctas`, tile `tile`) hold a piece of this pair and merges their partials.
 template <typename T, int D>
-__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeParams p, T* __restrict__ out) {
+__global__ void __launch_bounds__(D < 32 ? 32 : D) decode_combine_kernel(const DecodeParams p, T* __restrict__ out,
+                                                                       int n_ctas, int tile) {
+    __shared__ long long sh_before;
+    __shared__ Share sh_share;
     const int bh = blockIdx.x;
-    const int b = bh / p.H;
+    const int b = bh / p.H, h = bh - b * p.H;
     const int d = threadIdx.x;
-    const int n = seq_len_of(p, b);
-    const int nch = (n + p.chunk - 1) / p.chunk;
-    const size_t slot0 = static_cast<size_t>(bh) * p.c_max;
-    float m_all = -INFINITY;
-    for (int c = 0; c < nch; ++c) m_all = fmaxf(m_all, p.ws_ml[(slot0 + c) * 2]);
-    float l_all = 0.f, o = 0.f;
-    for (int c = 0; c < nch; ++c) {
-        const float wgt = exp2f(p.ws_ml[(slot0 + c) * 2] - m_all);
-        l_all += wgt * p.ws_ml[(slot0 + c) * 2 + 1];
-        o += wgt * p.ws_acc[(slot0 + c) * D + d];
+    if (threadIdx.x < 32) {
+        const Share s0 = share_of(p, 0, n_ctas, tile, threadIdx.x);
+        long long before = 0;
+        for (int i = threadIdx.x; i < b; i += 32) before += seq_len_of(p, i);
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) before += __shfl_xor_sync(0xffffffffu, before, off);
+        if (threadIdx.x == 0) {
+            sh_before = before;
+            sh_share = s0;
+        }
     }
-    out[static_cast<size_t>(bh) * D + d] = Elt<T>::from_float(nch > 0 ? o / l_all : 0.f);
+    __syncthreads();
+    if (d >= D) return;
+    const int n = seq_len_of(p, b);
+    const long long size = sh_share.size;
+    const long long pair_off = sh_before * p.H + static_cast<long long>(h) * n;
+    const long long total_end = pair_off + n;
+    float m_all = -INFINITY, l_all = 0.f, o = 0.f;
+    if (n > 0) {
+        const long long g_first = pair_off / size, g_last = (total_end - 1) / size;
+        const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
+        // first pass: the common maximum; second pass: the weighted sums
+        for (long long g = g_first; g <= g_last; ++g) {
+            int t0, t1;
+            piece_of(g * size, (g + 1) * size, pair_off, n, tile, t0, t1);
+            if (t0 < t1) m_all = fmaxf(m_all, p.ws_ml[(slot0 + (g - g_first)) * 2]);
+        }
+        for (long long g = g_first; g <= g_last; ++g) {
+            int t0, t1;
+            piece_of(g * size, (g + 1) * size, pair_off, n, tile, t0, t1);
+            if (t0 < t1) {
+                const size_t slot = slot0 + (g - g_first);
+                const float wgt = exp2f(p.ws_ml[slot * 2] - m_all);
+                l_all += wgt * p.ws_ml[slot * 2 + 1];
+                o += wgt * p.ws_acc[slot * D + d];
+            }
+        }
+    }
+    out[static_cast<size_t>(bh) * D + d] = Elt<T>::from_float(n > 0 ? o / l_all : 0.f);
 }
 
 // --------------------------------------------------------------------------------------
@@ -428,22 +542,13 @@ constexpr int default_tile(int row_bytes) {
     int t = 8192 / row_bytes;
     return t > 128 ? 128 : (t < 8 ? 8 : t);
 }
-// Smallest tile of any compiled variant for that row size (sizes the workspace).
-constexpr int smallest_tile(int row_bytes) { return row_bytes == 256 ? 16 : default_tile(row_bytes); }
 
-static int pick_chunk(int B, int H, int T_upper, int tile, int row_bytes, int grid_ctas) {
-    int forced = tune_get("decode_chunk");
-    if (forced > 0) return ((forced + tile - 1) / tile) * tile;
-    // Enough items to give every resident CTA several, but items long enough to amortise the
-    // per-item merge: between one tile and 256 KB of K rows.
-    long long tiles_total = static_cast<long long>(B) * H * ((T_upper + tile - 1) / tile);
-    long long per = tiles_total / (4ll * grid_ctas);
-    long long cap = (262144 / row_bytes) / tile;
-    if (cap < 1) cap = 1;
-    if (per > cap) per = cap;
-    if (per < 1) per = 1;
-    return static_cast<int>(per) * tile;
-}
+// Most CTAs per SM that a launch uses: the grid is persistent, more would only add partials.
+constexpr int kMaxCtasPerSm = 4;
+
+// Partial-result slots per (sequence, head) for a grid of `n_ctas`: a pair of n tokens overlaps at
+// most n / share + 2 shares, and n / share <= n_ctas / H because share >= H * sum(n_b) / n_ctas >= H * n / n_ctas.
+static int max_segments(int n_ctas, int H) { return (n_ctas + H - 1) / H + 2; }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -468,10 +573,15 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     }
     int per_sm = tune_get("decode_grid_per_sm");
     if (per_sm <= 0 || per_sm > ctas_per_sm[dev]) per_sm = ctas_per_sm[dev];
+    if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
     const int grid_full = device_sm_count() * per_sm;
+    // no more CTAs than tiles of work (upper bound from T_upper)
+    const long long tiles_upper = static_cast<long long>(p.B) * p.H * ((p.T_upper + TILE_T - 1) / TILE_T);
+    int grid = static_cast<int>(tiles_upper < grid_full ? tiles_upper : grid_full);
+    if (grid < 1) grid = 1;
+    p.max_seg = max_segments(grid, p.H);
+    p.l2_evict_first = tune_get("decode_l2_keep") ? 0 : 1;
 
-    p.chunk = pick_chunk(p.B, p.H, p.T_upper, TILE_T, Cfg::kRowBytes, grid_full);
-    p.c_max = (p.T_upper + p.chunk - 1) / p.chunk;
     // a bulk copy may cover several rows only when rows are adjacent in memory
     if (p.stride_t == D) {
         p.run_len = p.block_table ? (p.block_size < TILE_T ? p.block_size : TILE_T) : TILE_T;
@@ -480,22 +590,18 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     } else {
         p.run_len = 1;
     }
-    if (p.block_table && p.run_len > 1 && (p.chunk % p.run_len) != 0) p.run_len = 1;
 
-    const size_t slots = static_cast<size_t>(p.B) * p.H * p.c_max;
+    const size_t slots = static_cast<size_t>(p.B) * p.H * p.max_seg;
     const size_t acc_bytes = align_up(slots * D * sizeof(float), 256);
     const size_t need = acc_bytes + slots * 2 * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return B2KV_ERR_WORKSPACE;
     p.ws_acc = static_cast<float*>(workspace);
     p.ws_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
 
-    long long items_upper = static_cast<long long>(p.B) * p.H * p.c_max;
-    int grid = static_cast<int>(items_upper < grid_full ? items_upper : grid_full);
-    if (grid < 1) grid = 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(p);
     B2KV_CUDA_TRY(cudaGetLastError());
-    decode_combine_kernel<T, D><<<p.B * p.H, D, 0, s>>>(p, static_cast<T*>(out));
+    decode_combine_kernel<T, D><<<p.B * p.H, D < 32 ? 32 : D, 0, s>>>(p, static_cast<T*>(out), grid, TILE_T);
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
 }
@@ -512,7 +618,7 @@ static int dispatch_variant(const DecodeParams& p, void* out, void* ws, size_t w
             case 3: return launch_decode<T, D, 64, 4, 8>(p, out, ws, ws_bytes, stream);
             case 4: return launch_decode<T, D, 128, 3, 8>(p, out, ws, ws_bytes, stream);
             case 5: return launch_decode<T, D, 32, 6, 4>(p, out, ws, ws_bytes, stream);
-            case 6: return launch_decode<T, D, 64, 2, 8>(p, out, ws, ws_bytes, stream);
+            case 6: return launch_decode<T, D, 64, 3, 8>(p, out, ws, ws_bytes, stream);
             case 7: return launch_decode<T, D, 16, 6, 4>(p, out, ws, ws_bytes, stream);
             case 8: return launch_decode<T, D, 32, 4, 8>(p, out, ws, ws_bytes, stream);
             case 9: return launch_decode<T, D, 32, 4, 4>(p, out, ws, ws_bytes, stream);
@@ -523,8 +629,8 @@ static int dispatch_variant(const DecodeParams& p, void* out, void* ws, size_t w
             case 14: return launch_decode<T, D, 128, 2, 16>(p, out, ws, ws_bytes, stream);
             case 15: return launch_decode<T, D, 64, 3, 16>(p, out, ws, ws_bytes, stream);
             case 16: return launch_decode<T, D, 128, 2, 8>(p, out, ws, ws_bytes, stream);
-            // default: 16 KB tiles, 3 stages, 8 consumer warps, two CTAs per SM (best of the sweep)
-            default: return launch_decode<T, D, 64, 3, 8>(p, out, ws, ws_bytes, stream);
+            // default: 16 KB tiles, 2 stages, 8 consumer warps, three CTAs per SM (best of the sweep)
+            default: return launch_decode<T, D, 64, 2, 8>(p, out, ws, ws_bytes, stream);
         }
     } else {
         return launch_decode<T, D, default_tile(kRow), 4, 4>(p, out, ws, ws_bytes, stream);
@@ -591,14 +697,9 @@ extern "C" {
 size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype) {
     const int es = elt_bytes(dtype);
     if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0 || es == 0 || (D * es) % 16 != 0) return 0;
-    // An upper bound of what any compiled variant will ask for: the split is chosen as the launch
-    // chooses it, but for the smallest tile of that row size and for a grid larger than any
-    // variant's (16 CTAs per SM), both of which can only make the split finer.
-    const int row = D * es;
-    const int tile = smallest_tile(row);
-    const int chunk = pick_chunk(B, H, T_upper, tile, row, device_sm_count() * 16);
-    const size_t c_max = (static_cast<size_t>(T_upper) + chunk - 1) / chunk;
-    const size_t slots = static_cast<size_t>(B) * H * c_max;
+    // An upper bound of what any compiled variant will ask for: the largest grid a launch uses.
+    (void)T_upper;
+    const size_t slots = static_cast<size_t>(B) * H * max_segments(device_sm_count() * kMaxCtasPerSm, H);
     return align_up(slots * D * sizeof(float), 256) + slots * 2 * sizeof(float) + 256;
 }
 

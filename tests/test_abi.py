@@ -49,7 +49,7 @@ def test_status_text_and_version(pkg):
     with pytest.raises(pkg._native.B2KVError):
         pkg._native.check(-1)
     assert lib.b2kv_tune(b"no_such_knob", 1) == -1
-    assert lib.b2kv_tune(b"decode_chunk", 0) == 0
+    assert lib.b2kv_tune(b"decode_grid_per_sm", 0) == 0
 
 
 def test_argument_checks_return_before_any_launch(pkg):

@@ -58,14 +58,14 @@ def test_decode_microbench_and_paged_variant_full_size(pkg, ctx):
     del k_host, v_host
     np.testing.assert_allclose(U.to_f32(out), want, rtol=0, atol=2e-2)
 
-    # split invariance: another ring configuration and another split give the same result
+    # split invariance: another ring configuration and another grid (other cut points) give the same result
     pkg._native.tune("decode_variant", 9)
-    pkg._native.tune("decode_chunk", 256)
+    pkg._native.tune("decode_grid_per_sm", 1)
     try:
         out2 = _decode(pkg, ctx, cache, q)
     finally:
         pkg._native.tune("decode_variant", 0)
-        pkg._native.tune("decode_chunk", 0)
+        pkg._native.tune("decode_grid_per_sm", 0)
     assert float((out2.float() - out.float()).abs().max()) <= 4e-3
 
     # paged variant: the same logical content behind a seeded permutation of a 65536-block pool

@@ -210,12 +210,12 @@ def test_decode_uniform_length_mode_matches_ragged_mode(pkg, ctx):
     np.testing.assert_allclose(outs[0].numpy(), want, rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("variant,chunk", [(0, 0), (0, 64), (0, 1024), (1, 0), (2, 0), (3, 0), (4, 128), (5, 32),
-                                           (6, 0), (7, 16), (8, 0), (9, 0), (10, 0), (11, 0), (12, 0), (13, 0), (14, 0), (15, 0),
-                                           (16, 0)])
-def test_decode_kernel_variants_agree_with_oracle(pkg, ctx, variant, chunk):
+@pytest.mark.parametrize("variant,per_sm", [(0, 0), (0, 1), (0, 2), (1, 0), (2, 0), (3, 0), (4, 1), (5, 3), (6, 0),
+                                            (7, 4), (8, 0), (9, 0), (10, 0), (11, 0), (12, 0), (13, 0), (14, 0),
+                                            (15, 0), (16, 0)])
+def test_decode_kernel_variants_agree_with_oracle(pkg, ctx, variant, per_sm):
     pkg._native.tune("decode_variant", variant)
-    pkg._native.tune("decode_chunk", chunk)
+    pkg._native.tune("decode_grid_per_sm", per_sm)
     try:
         lens = [2048, 1, 1500, 31, 2000, 513]
         got, want = _decode_case(pkg, ctx, torch.bfloat16, "bhtd", 0, B=6, H=8, D=128, T_max=2048, lens=lens, seed=7)
@@ -224,7 +224,7 @@ def test_decode_kernel_variants_agree_with_oracle(pkg, ctx, variant, chunk):
         np.testing.assert_allclose(got, want, **U.TOL[torch.bfloat16])
     finally:
         pkg._native.tune("decode_variant", 0)
-        pkg._native.tune("decode_chunk", 0)
+        pkg._native.tune("decode_grid_per_sm", 0)
 
 
 def test_decode_softmax_weights_sum_to_one(pkg, ctx):
