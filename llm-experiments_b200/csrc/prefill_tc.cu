@@ -293,29 +293,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(0, 0);
             constexpr uint32_t idesc_pv = instr_desc(0, 1);
+            // Descriptors are built once; an MMA then only adds its byte offset (in 16-byte units) to
+            // the address field.  One thread issues every MMA of the CTA, so the instructions spent per
+            // issue bound the rate at which the tensor pipe can be fed.
+            const uint64_t dq0 = smem_desc(smem_u32(sm.q[0]), 16, 1024), dq1 = smem_desc(smem_u32(sm.q[1]), 16, 1024);
+            const uint64_t dk0 = smem_desc(smem_u32(sm.k[0]), 16, 1024), dk1 = smem_desc(smem_u32(sm.k[1]), 16, 1024);
+            const uint64_t dv0 = smem_desc(smem_u32(sm.v[0]), kHalfTileBytes, 1024);
+            const uint64_t dv1 = smem_desc(smem_u32(sm.v[1]), kHalfTileBytes, 1024);
+            static_assert(kStages == 2, "descriptor selection below assumes a two-stage ring");
             auto issue_qk = [&](int x, int j) {
-                const uint32_t q_addr = smem_u32(sm.q[x]);
-                const uint32_t k_addr = smem_u32(sm.k[j % kStages]);
+                const uint64_t dq = x ? dq1 : dq0;
+                const uint64_t dk = (j & 1) ? dk1 : dk0;
                 const uint32_t s_tmem = tmem + kColS + x * 128;
 #pragma unroll
                 for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint32_t off = kb * kHalfTileBytes + kk * 32;  // 16 bf16 of K = 32 bytes inside the span
-                        mma_ss(s_tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk,
-                               (kb | kk) ? 1u : 0u);
+                        // 16 elements of head_dim = 32 bytes inside the 128-byte swizzle span
+                        const uint64_t off = static_cast<uint64_t>((kb * kHalfTileBytes + kk * 32) >> 4);
+                        mma_ss(s_tmem, dq + off, dk + off, idesc_qk, (kb | kk) ? 1u : 0u);
                     }
                 }
                 mma_commit(&sm.s_full[x]);
             };
             auto issue_pv = [&](int x, int j) {
-                const uint32_t v_addr = smem_u32(sm.v[j % kStages]);
+                const uint64_t dv = (j & 1) ? dv1 : dv0;
                 const uint32_t p_tmem = tmem + kColS + x * 128;
+                const uint32_t o_tmem = tmem + kColO + x * 128;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    // 16 keys per step: 8 packed columns of P, 16 rows (2048 bytes) of V
-                    mma_ts(tmem + kColO + x * 128, p_tmem + kk * 8,
-                           smem_desc(v_addr + kk * 2048, kHalfTileBytes, 1024), idesc_pv, (j | kk) ? 1u : 0u);
+                    // 16 keys per MMA: 8 packed columns of P, 16 rows (2048 bytes) of V
+                    mma_ts(o_tmem, p_tmem + kk * 8, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                           (j | kk) ? 1u : 0u);
                 }
                 mma_commit(&sm.o_done[x]);
             };
