@@ -289,13 +289,22 @@ def run_b200(args, w, rank, world):
     def reset_lengths():
         gpu.kv_cache_set_lengths(cache, lens0)
 
+    fused = None
+    if head_split and args.fused_gather:
+        fused = sharding.FusedHeadGather(device, B, H_total, D, dtype)
+
     def step_device():
         gpu.batch_begin(ctx)
         gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
-        gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
+        if fused is not None:
+            full = fused.decode(ctx, cache, 0, q_b)  # merge kernel stores into every rank's buffer
+        else:
+            gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
+            full = None
         gpu.batch_commit(ctx)
-        if head_split and world > 1:
-            sharding.gather_heads(out_dev)  # [B, H_total*D] on every rank
+        if head_split and world > 1 and fused is None:
+            full = sharding.gather_heads(out_dev)  # NCCL all-gather: [B, H_total*D] on every rank
+        return full
 
     def barrier():
         if world > 1:
@@ -364,12 +373,9 @@ def run_b200(args, w, rank, world):
         gpu.gpu_buffer_2d_write(ctx, q_host, q_b)
         gpu.gpu_buffer_2d_write(ctx, nk_host, nk_b)
         gpu.gpu_buffer_2d_write(ctx, nv_host, nv_b)
-        gpu.batch_begin(ctx)
-        gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
-        gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
-        gpu.batch_commit(ctx)
-        if head_split and world > 1:
-            out_host_full.copy_(sharding.gather_heads(out_dev), non_blocking=True)
+        full = step_device()
+        if head_split and (world > 1 or fused is not None):
+            out_host_full.copy_(full, non_blocking=True)
             torch.cuda.current_stream().synchronize()
         else:
             gpu.gpu_buffer_2d_read(ctx, out_b, out_host)  # blocks until the result is on the host
@@ -410,7 +416,9 @@ def run_b200(args, w, rank, world):
         "data": "synthetic",
         "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": seqs_total,
                    "sum_len_rank0": int(np.sum(lens0)), "l2": "inputs (GBs of cache) far larger than L2, no flush",
-                   "parallelism": (f"heads split x{world}, one all-gather of the outputs per step" if head_split
+                   "parallelism": (f"heads split x{world}, outputs gathered "
+                                   + ("by peer stores fused into the merge kernel" if fused is not None
+                                      else "with one NCCL all-gather per step") if head_split
                                    else f"batch-sharded x{world}, no collective in the step")},
         "e2e": {"value": e2e_tps, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
@@ -565,6 +573,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="head-split workloads: gather the outputs with peer stores from the merge kernel instead of NCCL")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -123,6 +123,32 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
                       int dtype, void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream);
 
 /*
+ * Decode attention of the head-split configuration fused with the all-gather of its outputs.
+ * No counterpart in the reference (which is single-device).  Rank r of `world` ranks holds heads
+ * [r*H_local, (r+1)*H_local) of every sequence.  The merge kernel stores each output row
+ * straight into the [B, H_total*D] output buffers of ALL ranks (peer_out[w], peer-mapped device
+ * memory, plain stores over NVLink) at this rank's head offset; its last CTA then writes `epoch`
+ * into word `rank` of every rank's flag array (peer_flags[w]).  A final one-warp kernel waits, with
+ * a bound of about two seconds, until all `world` words of this rank's own flags (my_flags) have
+ * reached `epoch`; after it, peer_out[rank] holds the outputs of all heads, in stream order.
+ * (my_flags == NULL queues no wait kernel: the caller then orders the consumption itself.)
+ *   peer_out, peer_flags  device arrays of `world` pointers (the same on every rank up to
+ *                         address translation); flags are uint32[world], zeroed once.
+ *   counter               local uint32, zeroed once; counts finished merge CTAs for ever.
+ *   counter_target        value of the counter after this call = previous target + B*H_local
+ *                         (mod 2^32); epoch = number of this call, starting at 1.
+ * Use two output buffers alternately (by epoch parity): a rank may be one call ahead of a peer
+ * that still reads the previous result.  A wait that runs out sets B2KV_DEV_WAIT_TIMEOUT in
+ * dev_status and returns; nothing spins for ever.
+ */
+int b2kv_decode_allgather(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens, int len,
+                          int len_bias, int B, int H_local, int D, int T_upper, int64_t stride_b, int64_t stride_t,
+                          int64_t stride_h, int dtype, void* workspace, size_t workspace_bytes, void* const* peer_out,
+                          uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* counter,
+                          uint32_t counter_target, int rank, int world, int H_total, uint32_t epoch,
+                          int32_t* dev_status, void* stream);
+
+/*
  * b2kv_decode without a workspace argument.  It has no counterpart in the reference, whose
  * dispatch layer creates a fresh uniform buffer for every operation
  * (simple-llm/src/gpu/gpu_ops.py:184-203, :298) and so always allocates.

@@ -36,6 +36,19 @@ struct StageMeta {
     int pad;
 };
 
+// Optional epilogue of the merge kernel: instead of writing its row to a local output, every
+// CTA stores it straight into the output buffers of all ranks (peer memory over NVLink) at this
+// rank's head offset, and the last CTA to finish raises this rank's flag on every rank.
+struct GatherInfo {
+    void* const* peer_out;        // device array [world]: each rank's [B, h_total * D] output buffer (null = off)
+    uint32_t* const* peer_flags;  // device array [world]: each rank's flag words, one per source rank
+    const uint32_t* my_flags;     // this rank's own flag words (what the wait kernel watches)
+    unsigned int* counter;        // local: merge CTAs finished so far, never reset
+    unsigned int counter_target;  // value of the counter when this call's last CTA has finished
+    int rank, world, h_total;
+    uint32_t epoch;               // value written to the flags by this call
+};
+
 struct DecodeParams {
     const void* q;
     const void* k;
@@ -53,6 +66,7 @@ struct DecodeParams {
     int l2_evict_first;  // 1: K/V copies carry the evict-first L2 policy (each row is read once)
     int64_t stride_b, stride_t, stride_h;
     float q_prescale;
+    GatherInfo gather;
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
@@ -502,14 +516,12 @@ __global__ void __launch_bounds__(D < 32 ? 32 : D) decode_combine_kernel(const D
         }
     }
     __syncthreads();
-    if (d >= D) return;
     const int n = seq_len_of(p, b);
-    const long long size = sh_share.size;
-    const long long pair_off = sh_before * p.H + static_cast<long long>(h) * n;
-    const long long total_end = pair_off + n;
     float m_all = -INFINITY, l_all = 0.f, o = 0.f;
-    if (n > 0) {
-        const long long g_first = pair_off / size, g_last = (total_end - 1) / size;
+    if (d < D && n > 0) {
+        const long long size = sh_share.size;
+        const long long pair_off = sh_before * p.H + static_cast<long long>(h) * n;
+        const long long g_first = pair_off / size, g_last = (pair_off + n - 1) / size;
         const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
         // first pass: the common maximum; second pass: the weighted sums
         for (long long g = g_first; g <= g_last; ++g) {
@@ -528,7 +540,46 @@ __global__ void __launch_bounds__(D < 32 ? 32 : D) decode_combine_kernel(const D
             }
         }
     }
-    out[static_cast<size_t>(bh) * D + d] = Elt<T>::from_float(n > 0 ? o / l_all : 0.f);
+    const T val = Elt<T>::from_float(n > 0 ? o / l_all : 0.f);
+    if (p.gather.peer_out == nullptr) {
+        if (d < D) out[static_cast<size_t>(bh) * D + d] = val;
+        return;
+    }
+    // fused all-gather: the row goes to every rank's buffer, at this rank's heads
+    if (d < D) {
+        const size_t col = (static_cast<size_t>(b) * p.gather.h_total + static_cast<size_t>(p.gather.rank) * p.H + h) * D + d;
+        for (int w = 0; w < p.gather.world; ++w) static_cast<T*>(p.gather.peer_out[w])[col] = val;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int ticket = atomicAdd(p.gather.counter, 1u);
+        if (ticket + 1u == p.gather.counter_target) {
+            // every merge CTA of this call has stored and fenced its rows: publish
+            __threadfence_system();
+            for (int w = 0; w < p.gather.world; ++w) {
+                volatile uint32_t* flag = p.gather.peer_flags[w] + p.gather.rank;
+                *flag = p.gather.epoch;
+            }
+            __threadfence_system();
+        }
+    }
+}
+
+// Waits (bounded) until every rank's flag has reached `epoch`: lane w watches rank w.  The flags
+// are written by kernels running on other GPUs, never by a kernel queued behind this one.
+__global__ void gather_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int32_t* dev_status) {
+    const int w = threadIdx.x;
+    if (w >= world) return;
+    const volatile uint32_t* flag = flags + w;
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+        if (static_cast<int32_t>(*flag - epoch) >= 0) {
+            __threadfence_system();
+            return;
+        }
+        __nanosleep(it < 64 ? 100 : 1000);
+    }
+    report_status(dev_status, B2KV_DEV_WAIT_TIMEOUT);
 }
 
 // --------------------------------------------------------------------------------------
@@ -603,6 +654,10 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     B2KV_CUDA_TRY(cudaGetLastError());
     decode_combine_kernel<T, D><<<p.B * p.H, D < 32 ? 32 : D, 0, s>>>(p, static_cast<T*>(out), grid, TILE_T);
     B2KV_CUDA_TRY(cudaGetLastError());
+    if (p.gather.peer_out != nullptr && p.gather.my_flags != nullptr) {
+        gather_wait_kernel<<<1, 32, 0, s>>>(p.gather.my_flags, p.gather.world, p.gather.epoch, p.dev_status);
+        B2KV_CUDA_TRY(cudaGetLastError());
+    }
     return B2KV_OK;
 }
 
@@ -652,10 +707,10 @@ static int dispatch_dim(const DecodeParams& p, int D, void* out, void* ws, size_
 static int decode_entry(const void* q, const void* k, const void* v, void* out, const int32_t* seq_lens, int len,
                         int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
                         int H, int D, int T_upper, int64_t s0, int64_t st, int64_t sh, int dtype, void* workspace,
-                        size_t workspace_bytes, int32_t* dev_status, void* stream) {
+                        size_t workspace_bytes, int32_t* dev_status, void* stream, const GatherInfo* gather = nullptr) {
     const int es = elt_bytes(dtype);
     if (es == 0) return B2KV_ERR_UNSUPPORTED;
-    if (!q || !k || !v || !out) return B2KV_ERR_BAD_ARG;
+    if (!q || !k || !v || (!out && !gather)) return B2KV_ERR_BAD_ARG;
     if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0) return B2KV_ERR_BAD_ARG;
     if (static_cast<long long>(B) * H > 0x7fffffffLL / 4) return B2KV_ERR_UNSUPPORTED;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(workspace))
@@ -684,6 +739,7 @@ static int decode_entry(const void* q, const void* k, const void* v, void* out, 
     p.stride_t = st;
     p.stride_h = sh;
     p.q_prescale = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D)));
+    if (gather != nullptr) p.gather = *gather;
     if (dtype == B2KV_DTYPE_F32) return dispatch_dim<float>(p, D, out, workspace, workspace_bytes, stream);
     return dispatch_dim<__nv_bfloat16>(p, D, out, workspace, workspace_bytes, stream);
 }
@@ -721,6 +777,19 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
 }
 
 }  // extern "C"
+
+extern "C" int b2kv_decode_allgather(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
+                                     int len, int len_bias, int B, int H_local, int D, int T_upper, int64_t stride_b,
+                                     int64_t stride_t, int64_t stride_h, int dtype, void* workspace,
+                                     size_t workspace_bytes, void* const* peer_out, uint32_t* const* peer_flags,
+                                     const uint32_t* my_flags, uint32_t* counter, uint32_t counter_target, int rank,
+                                     int world, int H_total, uint32_t epoch, int32_t* dev_status, void* stream) {
+    if (!peer_out || !peer_flags || !counter) return B2KV_ERR_BAD_ARG;
+    if (world < 1 || world > 32 || rank < 0 || rank >= world || H_total != H_local * world) return B2KV_ERR_BAD_ARG;
+    GatherInfo g{peer_out, peer_flags, my_flags, counter, counter_target, rank, world, H_total, epoch};
+    return decode_entry(q, k_cache, v_cache, nullptr, seq_lens, len, len_bias, nullptr, 0, 0, 0, B, H_local, D, T_upper,
+                        stride_b, stride_t, stride_h, dtype, workspace, workspace_bytes, dev_status, stream, &g);
+}
 
 // --------------------------------------------------------------------------------------
 // Decode without any allocation by the caller: the split-K partials live in an array that is

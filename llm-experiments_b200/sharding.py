@@ -66,3 +66,89 @@ def head_split_decode(local_attention: Callable[[torch.Tensor], torch.Tensor], q
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     q_local = slice_heads(q_full, n_heads, head_dim, rank, world)
     return gather_heads(local_attention(q_local), group)
+
+
+class FusedHeadGather:
+    """Head-split decode whose all-gather is fused into the merge kernel (``b2kv_decode_allgather``).
+
+    Every rank owns ``H/W`` heads.  The merge kernel of each rank stores its output rows directly
+    into the ``[B, H*D]`` result buffers of all ranks over NVLink (symmetric memory obtained from
+    ``torch.distributed._symmetric_memory``), raises a flag on every rank, and a bounded wait on
+    the rank's own flags ends the call: no NCCL collective, no extra pass over the data.  Two
+    result buffers are used alternately, so a rank that runs one step ahead never overwrites a
+    result that a slower peer is still reading.
+    """
+
+    def __init__(self, device: torch.device, batch: int, n_heads_total: int, head_dim: int, dtype: torch.dtype,
+                 group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.B, self.H_total, self.D, self.dtype = batch, n_heads_total, head_dim, dtype
+        self.H_local = head_range(n_heads_total, self.rank, self.world)[1] - head_range(n_heads_total, self.rank,
+                                                                                           self.world)[0]
+        cols = n_heads_total * head_dim
+        self.out = symm_mem.empty((2, batch, cols), dtype=dtype, device=device)
+        self.flags = symm_mem.empty((self.world,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        out_hdl = symm_mem.rendezvous(self.out, group.group_name)
+        flag_hdl = symm_mem.rendezvous(self.flags, group.group_name)
+        buf_bytes = batch * cols * self.out.element_size()
+        self._setup_tables(device, [[int(ptr) + i * buf_bytes for ptr in out_hdl.buffer_ptrs] for i in range(2)],
+                           [int(ptr) for ptr in flag_hdl.buffer_ptrs])
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flags are zero before anyone writes them
+
+    @classmethod
+    def from_buffers(cls, device: torch.device, rank: int, world: int, batch: int, n_heads_total: int, head_dim: int,
+                     dtype: torch.dtype, out_buffers, flag_buffers):
+        """Builds a rank from buffers that the caller has already made visible to every rank
+        (its own peer mapping, or several emulated ranks on one device): ``out_buffers[w]`` is rank
+        w's ``[2, B, H*D]`` result tensor, ``flag_buffers[w]`` its zeroed ``int32[world]`` flags."""
+        self = object.__new__(cls)
+        self.rank, self.world = rank, world
+        self.B, self.H_total, self.D, self.dtype = batch, n_heads_total, head_dim, dtype
+        self.H_local = n_heads_total // world
+        self.out, self.flags = out_buffers[rank], flag_buffers[rank]
+        buf_bytes = batch * n_heads_total * head_dim * self.out.element_size()
+        self._setup_tables(device, [[t.data_ptr() + i * buf_bytes for t in out_buffers] for i in range(2)],
+                           [t.data_ptr() for t in flag_buffers])
+        return self
+
+    def _setup_tables(self, device, out_ptrs, flag_ptrs):
+        self._out_tables = [torch.tensor(ptrs, dtype=torch.int64, device=device) for ptrs in out_ptrs]
+        self._flag_table = torch.tensor(flag_ptrs, dtype=torch.int64, device=device)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.counter_target = 0
+
+    def decode(self, ctx, cache, layer_idx: int, q_local, wait: bool = True) -> torch.Tensor:
+        """Attention of this rank's heads over its cache slice; returns the ``[B, H*D]`` result of
+        all ranks (a view of the symmetric buffer used for this step)."""
+        from . import _native
+        from .batch import batch_op_begin, dev_status_ptr
+        from .kv_cache import cache_strides, decode_workspace, dtype_code
+
+        if cache.block_table is not None:
+            raise ValueError("the fused head gather takes contiguous caches")
+        if (cache.batch_size, cache.n_heads, cache.head_dim) != (self.B, self.H_local, self.D):
+            raise ValueError("cache does not hold this rank's heads")
+        if cache.current_len == 0:
+            raise ValueError("Cache is empty: current_len=0")
+        self.epoch = (self.epoch + 1) & 0xFFFFFFFF
+        self.counter_target = (self.counter_target + self.B * self.H_local) & 0xFFFFFFFF
+        buf = self.epoch & 1
+        ws = decode_workspace(cache)
+        stream = batch_op_begin(ctx)
+        s0, st, sh = cache_strides(cache)
+        layer = cache.layers[layer_idx]
+        rc = _native.lib.b2kv_decode_allgather(
+            q_local.buffer.data_ptr(), layer.k_cache.buffer.data_ptr(), layer.v_cache.buffer.data_ptr(),
+            None if cache.seq_lens is None else cache.seq_lens.data_ptr(), cache.current_len, 0, self.B, self.H_local,
+            self.D, min(cache.current_len, cache.max_seq_len), s0, st, sh, dtype_code(cache.dtype), ws.data_ptr(),
+            ws.numel(), self._out_tables[buf].data_ptr(), self._flag_table.data_ptr(),
+            self.flags.data_ptr() if wait else None, self.counter.data_ptr(), self.counter_target, self.rank,
+            self.world, self.H_total, self.epoch, dev_status_ptr(ctx), stream)
+        _native.check(rc)
+        return self.out[buf]
