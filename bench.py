@@ -559,7 +559,7 @@ def run_prefill(args, w, rank, world):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the split kernel per attended (token, head), from
-# the ncu capture of the 8-sequence case (profiles/decode_split_kernel_decode_small.md: 412.4 MB for
+# an ncu capture of the 8-sequence case (`--workload decode_small`: 412.4 MB for
 # 24908 tokens x 32 heads; the algorithmic figure is 512 B).  Traffic grows in proportion to the
 # tokens attended, so a full launch is this figure times its tokens and heads.
 DRAM_BYTES_PER_TOKEN_HEAD = 517.4

@@ -49,7 +49,9 @@ def softmax(x, axis=-1):
 
 
 def main():
-    ref_root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref_root = pathlib.Path(sys.argv[1])
     test_file = ref_root / "simple-llm" / "src" / "gpu_test.py"
     lines = test_file.read_text().splitlines(keepends=True)
     # Guard against a different revision of the reference: anchor lines must match.
