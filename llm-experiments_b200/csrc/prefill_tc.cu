@@ -454,6 +454,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tc_fence_before();
             mbar_arrive(&sm.p_ready[x]);
         }
+        // A parity wait cannot tell phase j from phase j - 2, so a thread that waits on o_done only now
+        // and then must not be more than one phase behind.  It is not: S of tile j exists only after
+        // QK^T(j), which was issued after PV(j - 1) into the in-order tensor pipe, so when this thread
+        // has finished tile n_x - 1 every PV up to n_x - 2 has completed.
         if (ok && n_x > 0) ok = mbar_wait(&sm.o_done[x], (n_x - 1) & 1);
         if (ok && n_x > 0) {
             tc_fence_after();
