@@ -198,7 +198,8 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
 
 /*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
- * "decode_grid_per_sm", "decode_l2_keep", "prefill_force_simt"); returns B2KV_ERR_BAD_ARG
+ * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
+ * "prefill_force_simt"); returns B2KV_ERR_BAD_ARG
  * for an unknown name.  Defaults are chosen per shape when a knob is 0.  No counterpart in
  * the reference beyond the tile-size fields of GPUConfig (gpu_types.py:69-121).
  */

@@ -20,8 +20,10 @@
 // HBM traffic per launch is the K and V rows of the attended tokens, once:
 // sum_b n_b * H * D * 2 * sizeof(element), plus q, out and the partials.
 #include <math.h>
+#include <string.h>
 
 #include "b2kv_common.cuh"
+#include "tma_map.cuh"
 
 namespace b2kv {
 
@@ -64,6 +66,8 @@ struct DecodeParams {
     int max_blocks, block_size, n_blocks;
     int run_len;  // tokens that one bulk copy may cover (contiguous in memory)
     int l2_evict_first;  // 1: K/V copies carry the evict-first L2 policy (each row is read once)
+    int use_tensor_map;  // 1: rows of a head are not adjacent in memory (reference layout): a tile is one tiled
+                         // TMA load through the kernel's tensor maps instead of one bulk copy per row
     int64_t stride_b, stride_t, stride_h;
     float q_prescale;
     GatherInfo gather;
@@ -78,7 +82,8 @@ template <typename T, int D, int TILE_T, int STAGES, int NCW>
 struct DecodeCfg {
     static constexpr int kRowBytes = D * static_cast<int>(sizeof(T));
     static constexpr int kTileBytes = TILE_T * kRowBytes;
-    static constexpr int kStageBytes = 2 * kTileBytes + kRowBytes;  // K tile, V tile, q row
+    // K tile, V tile, q row; stages start on 128-byte boundaries (tiled TMA destinations need that)
+    static constexpr int kStageBytes = (2 * kTileBytes + kRowBytes + 127) / 128 * 128;
     static constexpr int kChunksPerRow = kRowBytes / 16;
     static constexpr int kLanesPerRow = kChunksPerRow < 32 ? kChunksPerRow : 32;
     static constexpr int kChunksPerLane = kChunksPerRow / kLanesPerRow;
@@ -168,7 +173,8 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
 // --------------------------------------------------------------------------------------
 
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES>
-__device__ __forceinline__ void decode_producer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
+__device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUtensorMap* tm_k,
+                                                const CUtensorMap* tm_v, uint8_t* stages, uint64_t* full,
                                                 uint64_t* empty, StageMeta* meta, int lane) {
     const char* kbase = static_cast<const char*>(p.k);
     const char* vbase = static_cast<const char*>(p.v);
@@ -214,14 +220,26 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, uint8_t* 
                 mt.flags = (first ? kFlagFirst : 0) | (t0 + TILE_T >= t_end ? kFlagLast : 0);
                 mt.pad = 0;
                 meta[stage] = mt;
-                const uint32_t bytes =
-                    2u * static_cast<uint32_t>(ntok) * Cfg::kRowBytes + (first ? Cfg::kRowBytes : 0);
+                // a tiled load always delivers the whole box (rows past the end arrive as zeros or as
+                // the next rows of the cache; the consumers use the first ntok only)
+                const uint32_t rows = p.use_tensor_map ? static_cast<uint32_t>(TILE_T) : static_cast<uint32_t>(ntok);
+                const uint32_t bytes = 2u * rows * Cfg::kRowBytes + (first ? Cfg::kRowBytes : 0);
                 mbar_arrive_expect_tx(&full[stage], bytes);
             }
             __syncwarp();
             if (first && lane == 31) {
                 bulk_g2s(sbase + 2 * Cfg::kTileBytes,
                          qbase + (static_cast<size_t>(b) * p.H + h) * Cfg::kRowBytes, Cfg::kRowBytes, &full[stage]);
+            }
+            if (p.use_tensor_map) {
+                if (lane == 0) tma_load_4d(sbase, tm_k, &full[stage], 0, t0, h, b);
+                if (lane == 1) tma_load_4d(sbase + Cfg::kTileBytes, tm_v, &full[stage], 0, t0, h, b);
+                ++fills;
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+                continue;
             }
             const int nruns = (ntok + p.run_len - 1) / p.run_len;
             for (int r = lane; r < nruns; r += 32) {
@@ -469,7 +487,9 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
 }
 
 template <typename T, int D, int TILE_T, int STAGES, int NCW>
-__global__ void __launch_bounds__((NCW + 1) * 32) decode_split_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__((NCW + 1) * 32)
+decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v) {
     using Cfg = DecodeCfg<T, D, TILE_T, STAGES, NCW>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -488,7 +508,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32) decode_split_kernel(const Deco
     }
     __syncthreads();
     if (warp == NCW) {
-        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, stages, full, empty, meta, lane);
+        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, lane);
     } else {
         decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, meta, merge, warp, lane);
     }
@@ -649,8 +669,23 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     p.ws_acc = static_cast<float*>(workspace);
     p.ws_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
 
+    // Row-strided contiguous caches (the reference layout): one tiled TMA load per tile.  The maps
+    // bound the token coordinate by T_upper, which no attended row exceeds.
+    CUtensorMap tm_k, tm_v;
+    memset(&tm_k, 0, sizeof(tm_k));
+    memset(&tm_v, 0, sizeof(tm_v));
+    p.use_tensor_map = 0;
+    if (p.block_table == nullptr && p.run_len == 1 && !tune_get("decode_no_tensor_map") && D <= 256) {
+        const int dt = sizeof(T) == 4 ? B2KV_DTYPE_F32 : B2KV_DTYPE_BF16;
+        if (make_cache_tensor_map(&tm_k, p.k, dt, D, p.T_upper, p.H, p.B, p.stride_b, p.stride_t, p.stride_h, D, TILE_T,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE) &&
+            make_cache_tensor_map(&tm_v, p.v, dt, D, p.T_upper, p.H, p.B, p.stride_b, p.stride_t, p.stride_h, D, TILE_T,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE))
+            p.use_tensor_map = 1;
+    }
+
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(p);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(p, tm_k, tm_v);
     B2KV_CUDA_TRY(cudaGetLastError());
     decode_combine_kernel<T, D><<<p.B * p.H, D < 32 ? 32 : D, 0, s>>>(p, static_cast<T*>(out), grid, TILE_T);
     B2KV_CUDA_TRY(cudaGetLastError());

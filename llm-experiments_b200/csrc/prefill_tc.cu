@@ -23,10 +23,10 @@
 // TMEM columns: S_A 0-127, S_B 128-255, O_A 256-383, O_B 384-511 (all 512).
 // Every mbarrier wait is bounded; a wait that runs out makes all warps fall through to the
 // common exit, where the tensor memory is released.
-#include <cuda.h>
 #include <math.h>
 
 #include "prefill.cuh"
+#include "tma_map.cuh"
 
 namespace b2kv {
 
@@ -502,26 +502,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 // View of a [B*N, H*D] bf16 matrix as (x = column, y = row inside the sequence, z = sequence), so
 // that rows past the end of a sequence read as zero instead of the next sequence's rows.
 static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = tensor_map_encoder();
     if (fn == nullptr) return false;
     const cuuint64_t dims[3] = {static_cast<cuuint64_t>(E), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(B)};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(E) * 2, static_cast<cuuint64_t>(N) * E * 2};
@@ -530,22 +514,6 @@ static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E) {
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// View of a cache of any layout as (d, token, head, sequence), cut to the first N tokens so that a
-// store of a partly filled tile leaves the rows past the sequence end untouched.
-static bool make_cache_map(CUtensorMap* map, void* base, int B, int N, int H, int64_t sb, int64_t st, int64_t sh) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(H),
-                                static_cast<cuuint64_t>(B)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st) * 2, static_cast<cuuint64_t>(sh) * 2,
-                                   static_cast<cuuint64_t>(sb) * 2};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
-           CUDA_SUCCESS;
 }
 
 }  // namespace tc
@@ -563,8 +531,12 @@ int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) 
     if (p.k_cache != nullptr) {
         // a cache whose strides a tensor map cannot express goes to the SIMT kernel
         if (p.stride_t < D || p.stride_h <= 0 || p.stride_b <= 0) return B2KV_ERR_UNSUPPORTED;
-        if (!tc::make_cache_map(&tkc, p.k_cache, p.B, p.N, p.H, p.stride_b, p.stride_t, p.stride_h) ||
-            !tc::make_cache_map(&tvc, p.v_cache, p.B, p.N, p.H, p.stride_b, p.stride_t, p.stride_h))
+        // cut to the first N tokens, so that a store of a partly filled tile leaves the rows past the
+        // sequence end untouched
+        if (!make_cache_tensor_map(&tkc, p.k_cache, dtype, D, p.N, p.H, p.B, p.stride_b, p.stride_t, p.stride_h, 64,
+                                   128, CU_TENSOR_MAP_SWIZZLE_128B) ||
+            !make_cache_tensor_map(&tvc, p.v_cache, dtype, D, p.N, p.H, p.B, p.stride_b, p.stride_t, p.stride_h, 64,
+                                   128, CU_TENSOR_MAP_SWIZZLE_128B))
             return B2KV_ERR_UNSUPPORTED;
     } else {
         tkc = tk;  // never dereferenced when no cache is given
