@@ -181,8 +181,9 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void*
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until the committed stores have completed.
-__device__ __forceinline__ void tma_store_wait() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Waits until the committed stores have finished reading shared memory (the CTA may then exit;
+// the writes themselves complete before the kernel does).
+__device__ __forceinline__ void tma_store_wait() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 // 128 consecutive fp32 columns of this thread's TMEM lane, as four 32-column loads in flight together.
 __device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
