@@ -259,7 +259,9 @@ def run_b200(args, w, rank, world):
     E = H * D
     dtype = torch.bfloat16
     lens0 = make_lengths(w, 0 if head_split else rank)  # rank 0 draws the seed-0 lengths of the named config
-    T_max = int(lens0.max()) + SLACK
+    # head-room for the rows appended by the longest timed loop (lengths are reset between loops)
+    slack = max(SLACK, args.steps + max(3, args.warmup) + 64)
+    T_max = int(lens0.max()) + slack
     n_blocks = 0
     if bs:
         max_blocks = (T_max + bs - 1) // bs
@@ -329,8 +331,6 @@ def run_b200(args, w, rank, world):
         return ms
 
     steps, warm = args.steps, max(3, args.warmup)
-    if steps + warm + 8 > SLACK // 2:
-        raise SystemExit(f"steps + warmup must stay below {SLACK // 2 - 8} (cache head-room)")
 
     # ---- value: inputs resident in HBM -------------------------------------------------
     reset_lengths()
