@@ -80,3 +80,41 @@ def test_single_rank_waits_on_its_own_flag(pkg):
     torch.cuda.synchronize()
     assert int(ctx.dev_status.item()) == 0  # the wait found its flag, no timeout
     np.testing.assert_allclose(U.to_f32(res), U.oracle_decode(q, k_log, v_log, lens), **U.TOL[dtype])
+
+
+def test_wait_that_nobody_answers_runs_out_and_reports(pkg):
+    """Failure detection without a fault: rank 0 of two waits for a peer that never runs.  The
+    bounded wait gives up after about two seconds, records B2KV_DEV_WAIT_TIMEOUT in the status word
+    and returns; the context stays usable and the rank's own rows are in place."""
+    import time
+
+    from llm_experiments_b200 import sharding
+
+    ctx = U.make_ctx(pkg)
+    gpu = pkg.gpu
+    dev = ctx.device
+    world, B, H, D, T_max, dtype = 2, 2, 4, 128, 128, torch.bfloat16
+    Hl = H // world
+    k_log = U.randn((B, T_max, H, D), dtype, dev, 1)
+    v_log = U.randn((B, T_max, H, D), dtype, dev, 2)
+    outs = [torch.zeros((2, B, H * D), dtype=dtype, device=dev) for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
+    rank0 = sharding.FusedHeadGather.from_buffers(dev, 0, world, B, H, D, dtype, outs, flags)
+    cache = _make_cache(pkg, ctx, B, Hl, D, T_max, dtype, k_log[:, :, :Hl].contiguous(), v_log[:, :, :Hl].contiguous(),
+                        [T_max, 5])
+    q = U.randn((B, H * D), dtype, dev, 3)
+    ctx.dev_status = None
+    t0 = time.perf_counter()
+    gpu.batch_begin(ctx)
+    res = rank0.decode(ctx, cache, 0, U.buf2d(pkg, ctx, sharding.slice_heads(q, H, D, 0, world)))
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert int(ctx.dev_status.item()) == 3  # B2KV_DEV_WAIT_TIMEOUT: rank 1's flag never came
+    assert 0.2 < waited < 30.0
+    ctx.dev_status.zero_()
+    assert flags[0].cpu().tolist() == [1, 0] and flags[1].cpu().tolist() == [1, 0]
+    want = U.oracle_decode(q, k_log, v_log, [T_max, 5]).reshape(B, H, D)[:, :Hl].reshape(B, Hl * D)
+    np.testing.assert_allclose(U.to_f32(res[:, : Hl * D]), want, **U.TOL[dtype])
+    # the device still works
+    assert float(torch.ones(4, device=dev).sum()) == 4.0

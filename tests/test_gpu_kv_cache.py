@@ -291,3 +291,21 @@ def test_multi_layer_decode_loop_with_the_reference_quirk(pkg, ctx):
         view = U.logical_view(cache, cache.layers[l], "k")
         for t in range(3):
             assert torch.equal(view[:, t].reshape(B, E), ks[t][l])
+
+
+def test_batch_commit_raises_on_device_status_when_asked(pkg, ctx):
+    gpu = pkg.gpu
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=1, max_seq_len=32, n_layers=1, n_heads=2,
+                                                       head_dim=16, block_size=16, n_blocks=2))
+    cache.block_table[0, 0] = 5  # outside the pool
+    nk = U.randn((1, 32), torch.float32, ctx.device, 1)
+    ctx.dev_status = None
+    ctx.config.check_device_status = True
+    try:
+        gpu.batch_begin(ctx)
+        gpu.kv_cache_update(ctx, cache, 0, U.buf2d(pkg, ctx, nk), U.buf2d(pkg, ctx, nk))
+        with pytest.raises(RuntimeError, match="block-table entry points outside the pool"):
+            gpu.batch_commit(ctx)
+        assert int(ctx.dev_status.item()) == 0  # cleared after it was reported
+    finally:
+        ctx.config.check_device_status = False
