@@ -85,3 +85,34 @@ def test_shard_ranges_cover_everything(pkg):
         sharding.head_range(6, 0, 4)
     with pytest.raises(ValueError):
         sharding.shard_range(4, 2, 2)
+
+
+def _worker_missing_rank(rank, world, port, out_dir):
+    import datetime
+    import time
+
+    import __graft_entry__
+
+    __graft_entry__.import_package()
+    from llm_experiments_b200 import sharding
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    if rank == 0:
+        try:
+            sharding.gather_heads(torch.zeros(2, 8))
+            outcome = "completed"
+        except Exception as exc:  # the collective gives up instead of waiting for ever
+            outcome = "error: " + type(exc).__name__
+        with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+            f.write(outcome)
+    else:
+        time.sleep(8)  # this rank never joins the exchange
+    os._exit(0)  # skip the group shutdown: it would wait for the rank that never joined
+
+
+def test_rank_that_never_joins_ends_the_collective_with_an_error(tmp_path):
+    world = 2
+    mp.spawn(_worker_missing_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / "rank0.txt").read_text().startswith("error")
