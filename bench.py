@@ -258,7 +258,9 @@ def run_b200(args, w, rank, world):
         H = h1 - h0
     E = H * D
     dtype = torch.bfloat16
-    lens0 = make_lengths(w, 0 if head_split else rank)  # rank 0 draws the seed-0 lengths of the named config
+    # every rank holds its own batch (own K/V/q values) with the seed-0 lengths of the named configuration,
+    # so that the work per GPU is the same at every N (weak scaling)
+    lens0 = make_lengths(w, 0)
     # head-room for the rows appended by the longest timed loop (lengths are reset between loops)
     slack = max(SLACK, args.steps + max(3, args.warmup) + 64)
     T_max = int(lens0.max()) + slack
