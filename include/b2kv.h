@@ -190,7 +190,7 @@ int b2kv_decode_static(const void* q, const void* k_cache, const void* v_cache, 
  * j <= i.  When k_cache / v_cache are non-NULL the kernel also writes K / V rows 0..N-1 of
  * every sequence into the caches (same dtype, layout given by the cache strides), which
  * the reference can only do one token at a time through kv_cache_update.
- * bf16 with D == 128 runs on the tcgen05 tensor cores; other shapes run on a SIMT kernel.
+ * bf16 with D == 128 or 64 runs on the tcgen05 tensor cores; other shapes run on a SIMT kernel.
  */
 int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache,
                  void* v_cache, int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B, int N, int H,

@@ -1,4 +1,4 @@
-// Causal flash-attention prefill on the Blackwell tensor cores: bf16, head_dim 128.
+// Causal flash-attention prefill on the Blackwell tensor cores: bf16, head_dim 128 or 64.
 //
 // The reference kernel (simple-llm/src/gpu/gpu_kernels.py:499-770) computes the same tiled
 // online softmax with scalar fp32 dot products from workgroup memory.  Here QK^T and PV are
@@ -34,16 +34,16 @@ namespace tc {
 
 constexpr int kTileM = 128;   // query rows per tile (two tiles per CTA)
 constexpr int kBlockN = 128;  // keys per K/V tile
-constexpr int kD = 128;
 constexpr int kStages = 2;                      // K ring and V ring depth
 constexpr int kHalfTileBytes = 128 * 128;       // 128 rows x 64 bf16 (one 128-byte swizzle span per row)
-constexpr int kTileBytes = 2 * kHalfTileBytes;  // 128 x 128 bf16
 constexpr int kThreads = 320;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256;       // + 128 for tile B
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
+template <int kD>
 struct SharedStorage {
+    static constexpr int kTileBytes = (kD / 64) * kHalfTileBytes;  // 128 rows x kD bf16
     alignas(1024) uint8_t q[2][kTileBytes];
     alignas(1024) uint8_t k[kStages][kTileBytes];
     alignas(1024) uint8_t v[kStages][kTileBytes];
@@ -96,10 +96,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
     return d;
 }
 
-// Instruction descriptor: fp32 accumulate, bf16 A and B, M = N = 128.
-__host__ __device__ constexpr uint32_t instr_desc(int a_mn_major, int b_mn_major) {
+// Instruction descriptor: fp32 accumulate, bf16 A and B, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int a_mn_major, int b_mn_major, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
-           (static_cast<uint32_t>(b_mn_major) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+           (static_cast<uint32_t>(b_mn_major) << 16) | ((static_cast<uint32_t>(n) >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]
@@ -194,13 +194,16 @@ __device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t (&r)[128]) {
     }
 }
 
+template <int kD>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kc,
                   const __grid_constant__ CUtensorMap tm_vc, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
-    SharedStorage& sm =
-        *reinterpret_cast<SharedStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using Smem = SharedStorage<kD>;
+    constexpr int kHalves = kD / 64;  // 64-column (128-byte) spans per row
+    constexpr int kTileBytes = Smem::kTileBytes;
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_cb = (p.N + 2 * kTileM - 1) / (2 * kTileM);
@@ -244,11 +247,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (lane == 0) {
             const int x0 = h * kD;
             mbar_arrive_expect_tx(&sm.q_full, (n_b > 0 ? 2 : 1) * kTileBytes);
-            tma_load_3d(sm.q[0], &tm_q, &sm.q_full, x0, q0, b);
-            tma_load_3d(sm.q[0] + kHalfTileBytes, &tm_q, &sm.q_full, x0 + 64, q0, b);
-            if (n_b > 0) {
-                tma_load_3d(sm.q[1], &tm_q, &sm.q_full, x0, q0 + kTileM, b);
-                tma_load_3d(sm.q[1] + kHalfTileBytes, &tm_q, &sm.q_full, x0 + 64, q0 + kTileM, b);
+#pragma unroll
+            for (int hf = 0; hf < kHalves; ++hf) {
+                tma_load_3d(sm.q[0] + hf * kHalfTileBytes, &tm_q, &sm.q_full, x0 + hf * 64, q0, b);
+                if (n_b > 0) tma_load_3d(sm.q[1] + hf * kHalfTileBytes, &tm_q, &sm.q_full, x0 + hf * 64, q0 + kTileM, b);
             }
             bool ok = true;
             for (int j = 0; j < n_max && ok; ++j) {
@@ -257,13 +259,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 ok = mbar_wait(&sm.k_empty[st], par);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
-                tma_load_3d(sm.k[st], &tm_k, &sm.k_full[st], x0, j * kBlockN, b);
-                tma_load_3d(sm.k[st] + kHalfTileBytes, &tm_k, &sm.k_full[st], x0 + 64, j * kBlockN, b);
+#pragma unroll
+                for (int hf = 0; hf < kHalves; ++hf)
+                    tma_load_3d(sm.k[st] + hf * kHalfTileBytes, &tm_k, &sm.k_full[st], x0 + hf * 64, j * kBlockN, b);
                 ok = mbar_wait(&sm.v_empty[st], par);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
-                tma_load_3d(sm.v[st], &tm_v, &sm.v_full[st], x0, j * kBlockN, b);
-                tma_load_3d(sm.v[st] + kHalfTileBytes, &tm_v, &sm.v_full[st], x0 + 64, j * kBlockN, b);
+#pragma unroll
+                for (int hf = 0; hf < kHalves; ++hf)
+                    tma_load_3d(sm.v[st] + hf * kHalfTileBytes, &tm_v, &sm.v_full[st], x0 + hf * 64, j * kBlockN, b);
             }
             // The CTA's own K / V rows are the last one (A only) or two K/V tiles; they are still in
             // the rings.  Once the MMAs that read a tile have completed (its "empty" barrier), store
@@ -273,15 +277,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const int st = t % kStages;
                     ok = mbar_wait(&sm.k_empty[st], (t / kStages) & 1);
                     if (!ok) break;
-                    tma_store_4d(&tm_kc, sm.k[st], 0, t * kBlockN, h, b);
-                    tma_store_4d(&tm_kc, sm.k[st] + kHalfTileBytes, 64, t * kBlockN, h, b);
+#pragma unroll
+                    for (int hf = 0; hf < kHalves; ++hf)
+                        tma_store_4d(&tm_kc, sm.k[st] + hf * kHalfTileBytes, hf * 64, t * kBlockN, h, b);
                 }
                 for (int t = qa; t < n_max && ok; ++t) {
                     const int st = t % kStages;
                     ok = mbar_wait(&sm.v_empty[st], (t / kStages) & 1);
                     if (!ok) break;
-                    tma_store_4d(&tm_vc, sm.v[st], 0, t * kBlockN, h, b);
-                    tma_store_4d(&tm_vc, sm.v[st] + kHalfTileBytes, 64, t * kBlockN, h, b);
+#pragma unroll
+                    for (int hf = 0; hf < kHalves; ++hf)
+                        tma_store_4d(&tm_vc, sm.v[st] + hf * kHalfTileBytes, hf * 64, t * kBlockN, h, b);
                 }
                 tma_store_commit();
                 tma_store_wait();
@@ -292,8 +298,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc(0, 0);
-            constexpr uint32_t idesc_pv = instr_desc(0, 1);
+            constexpr uint32_t idesc_qk = instr_desc(0, 0, kBlockN);  // S[128 x 128 keys]
+            constexpr uint32_t idesc_pv = instr_desc(0, 1, kD);       // O[128 x kD]
             // Descriptors are built once; an MMA then only adds its byte offset (in 16-byte units) to
             // the address field.  One thread issues every MMA of the CTA, so the instructions spent per
             // issue bound the rate at which the tensor pipe can be fed.
@@ -307,7 +313,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint64_t dk = (j & 1) ? dk1 : dk0;
                 const uint32_t s_tmem = tmem + kColS + x * 128;
 #pragma unroll
-                for (int kb = 0; kb < 2; ++kb) {
+                for (int kb = 0; kb < kHalves; ++kb) {
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
                         // 16 elements of head_dim = 32 bytes inside the 128-byte swizzle span
@@ -441,7 +447,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (ok) {
                     tc_fence_after();
 #pragma unroll 1
-                    for (int cc = 0; cc < 4; ++cc) {
+                    for (int cc = 0; cc < kD / 32; ++cc) {
                         uint32_t o[32];
                         tmem_ld32(o_tmem + cc * 32, o);
                         tmem_wait_ld();
@@ -468,7 +474,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             __nv_bfloat16* Og =
                 static_cast<__nv_bfloat16*>(p.O) + (static_cast<size_t>(b) * p.N + grow) * E + static_cast<size_t>(h) * kD;
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < kD / 32; ++cc) {
                 uint32_t o[32];
                 tmem_ld32(o_tmem + cc * 32, o);
                 tmem_wait_ld();
@@ -519,8 +525,9 @@ static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E) {
 
 }  // namespace tc
 
-int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) {
-    if (dtype != B2KV_DTYPE_BF16 || D != tc::kD) return B2KV_ERR_UNSUPPORTED;
+template <int kD>
+static int launch_prefill_tc(const PrefillParams& p, int dtype, void* stream) {
+    constexpr int D = kD;
     const int E = p.H * D;
     const long long n_cb = (p.N + 2 * tc::kTileM - 1) / (2 * tc::kTileM);
     const long long ctas = n_cb * p.H * p.B;
@@ -543,20 +550,26 @@ int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) 
         tkc = tk;  // never dereferenced when no cache is given
         tvc = tv;
     }
-    constexpr size_t smem = sizeof(tc::SharedStorage) + 1024;
+    constexpr size_t smem = sizeof(tc::SharedStorage<kD>) + 1024;
+    auto kernel = tc::prefill_tc_kernel<kD>;
     static bool configured[64] = {false};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
     if (!configured[dev]) {
-        B2KV_CUDA_TRY(cudaFuncSetAttribute(tc::prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem)));
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         configured[dev] = true;
     }
-    tc::prefill_tc_kernel<<<static_cast<unsigned>(ctas), tc::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-        tq, tk, tv, tkc, tvc, p);
+    kernel<<<static_cast<unsigned>(ctas), tc::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, tkc, tvc, p);
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
+}
+
+int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream) {
+    if (dtype != B2KV_DTYPE_BF16) return B2KV_ERR_UNSUPPORTED;
+    if (D == 128) return launch_prefill_tc<128>(p, dtype, stream);
+    if (D == 64) return launch_prefill_tc<64>(p, dtype, stream);
+    return B2KV_ERR_UNSUPPORTED;
 }
 
 }  // namespace b2kv
