@@ -309,3 +309,29 @@ def test_batch_commit_raises_on_device_status_when_asked(pkg, ctx):
         assert int(ctx.dev_status.item()) == 0  # cleared after it was reported
     finally:
         ctx.config.check_device_status = False
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_decode_random_shapes_against_oracle(pkg, ctx, seed):
+    """Randomised shapes: batch, heads, head_dim, storage type, layout, block size and ragged
+    lengths (with empty sequences) drawn from a seeded generator."""
+    rng = np.random.default_rng(1000 + seed)
+    dtype = [torch.float32, torch.bfloat16][int(rng.integers(0, 2))]
+    D = int(rng.choice([16, 32, 64, 128, 256]))
+    B = int(rng.integers(1, 71))
+    H = int(rng.integers(1, 10))
+    T_max = int(rng.choice([1, 7, 64, 65, 200, 1025, 3000]))
+    if B * H * T_max * D > 60_000_000:  # keep the oracle quick
+        B = max(1, 60_000_000 // (H * T_max * D))
+    layout, block_size = [("bthd", 0), ("bhtd", 0), ("bhtd", 16), ("bhtd", 32), ("bhtd", 5)][int(rng.integers(0, 5))]
+    lens = rng.integers(0, T_max + 1, size=B)
+    if rng.random() < 0.3:
+        lens[rng.integers(0, B)] = 0
+    lens[rng.integers(0, B)] = T_max  # at least one full sequence
+    got, want = _decode_case(pkg, ctx, dtype, layout, block_size, B=B, H=H, D=D, T_max=T_max, lens=lens.tolist(),
+                             seed=seed)
+    assert np.isfinite(got).all()
+    for b in range(B):
+        if lens[b] == 0:
+            assert np.all(got[b] == 0.0)
+    np.testing.assert_allclose(got, want, **U.TOL[dtype])
