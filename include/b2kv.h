@@ -149,6 +149,21 @@ int b2kv_decode_allgather(const void* q, const void* k_cache, const void* v_cach
                           int32_t* dev_status, void* stream);
 
 /*
+ * Decode attention over a SLICE of every sequence's tokens, for the sequence-split
+ * (context-parallel) configuration in which each rank holds part of a long cache; no counterpart
+ * in the reference.  b2kv_decode_partial is b2kv_decode except that it leaves, per (sequence, head),
+ * the unnormalised row and its softmax statistics in partial_out (float [B*H, D + 2]: D sums,
+ * then the maximum in the log2 domain, -inf for an empty slice, then the sum of weights).
+ * b2kv_merge_partials combines R such arrays (parts [R, B*H, D + 2], e.g. all-gathered from R ranks)
+ * into the normalised output [B, H*D] of type dtype.
+ */
+int b2kv_decode_partial(const void* q, const void* k_cache, const void* v_cache, float* partial_out,
+                        const int32_t* seq_lens, int len, int len_bias, int B, int H, int D, int T_upper,
+                        int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype, void* workspace,
+                        size_t workspace_bytes, int32_t* dev_status, void* stream);
+int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* out, int dtype, void* stream);
+
+/*
  * b2kv_decode without a workspace argument.  It has no counterpart in the reference, whose
  * dispatch layer creates a fresh uniform buffer for every operation
  * (simple-llm/src/gpu/gpu_ops.py:184-203, :298) and so always allocates.

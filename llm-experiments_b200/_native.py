@@ -49,6 +49,9 @@ SIGNATURES = {
                                _i, _vp, _sz, _vp, _vp]),
     "b2kv_decode_allgather": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _sz, _vp, _vp,
                                    _vp, _vp, ctypes.c_uint32, _i, _i, _i, ctypes.c_uint32, _vp, _vp]),
+    "b2kv_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _sz, _vp,
+                                 _vp]),
+    "b2kv_merge_partials": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "b2kv_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp]),
     "b2kv_tune": (_i, [ctypes.c_char_p, _i]),

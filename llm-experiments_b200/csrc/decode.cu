@@ -71,6 +71,7 @@ struct DecodeParams {
     int64_t stride_b, stride_t, stride_h;
     float q_prescale;
     GatherInfo gather;
+    float* partial_out;  // non-null: the merge kernel writes (unnormalised row, max, sum) instead of the output
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
@@ -560,6 +561,17 @@ __global__ void __launch_bounds__(D < 32 ? 32 : D) decode_combine_kernel(const D
             }
         }
     }
+    if (p.partial_out != nullptr) {
+        // sequence-split mode: this rank saw only a slice of the tokens; hand the unnormalised row and
+        // its (max, sum) to the cross-rank merge.  Layout [B*H, D + 2]; max is in the log2 domain.
+        float* row = p.partial_out + static_cast<size_t>(bh) * (D + 2);
+        if (d < D) row[d] = o;
+        if (d == 0) {
+            row[D] = m_all;
+            row[D + 1] = l_all;
+        }
+        return;
+    }
     const T val = Elt<T>::from_float(n > 0 ? o / l_all : 0.f);
     if (p.gather.peer_out == nullptr) {
         if (d < D) out[static_cast<size_t>(bh) * D + d] = val;
@@ -742,7 +754,8 @@ static int dispatch_dim(const DecodeParams& p, int D, void* out, void* ws, size_
 static int decode_entry(const void* q, const void* k, const void* v, void* out, const int32_t* seq_lens, int len,
                         int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
                         int H, int D, int T_upper, int64_t s0, int64_t st, int64_t sh, int dtype, void* workspace,
-                        size_t workspace_bytes, int32_t* dev_status, void* stream, const GatherInfo* gather = nullptr) {
+                        size_t workspace_bytes, int32_t* dev_status, void* stream, const GatherInfo* gather = nullptr,
+                        float* partial_out = nullptr) {
     const int es = elt_bytes(dtype);
     if (es == 0) return B2KV_ERR_UNSUPPORTED;
     if (!q || !k || !v || (!out && !gather)) return B2KV_ERR_BAD_ARG;
@@ -775,6 +788,7 @@ static int decode_entry(const void* q, const void* k, const void* v, void* out, 
     p.stride_h = sh;
     p.q_prescale = static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D)));
     if (gather != nullptr) p.gather = *gather;
+    p.partial_out = partial_out;
     if (dtype == B2KV_DTYPE_F32) return dispatch_dim<float>(p, D, out, workspace, workspace_bytes, stream);
     return dispatch_dim<__nv_bfloat16>(p, D, out, workspace, workspace_bytes, stream);
 }
@@ -812,6 +826,58 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
 }
 
 }  // extern "C"
+
+namespace b2kv {
+
+// Merges R partial results of every (sequence, head): parts[r][bh][0..D) unnormalised row,
+// [D] max (log2 domain, -inf when the slice held no token), [D+1] sum.  One CTA per (sequence, head).
+template <typename T>
+__global__ void merge_partials_kernel(const float* __restrict__ parts, int R, int BH, int D, T* __restrict__ out) {
+    const int bh = blockIdx.x;
+    const size_t stride_r = static_cast<size_t>(BH) * (D + 2);
+    const float* base = parts + static_cast<size_t>(bh) * (D + 2);
+    float m_all = -INFINITY;
+    for (int r = 0; r < R; ++r) m_all = fmaxf(m_all, base[r * stride_r + D]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float l_all = 0.f, o = 0.f;
+        if (m_all != -INFINITY) {
+            for (int r = 0; r < R; ++r) {
+                const float m_r = base[r * stride_r + D];
+                if (m_r == -INFINITY) continue;
+                const float w = exp2f(m_r - m_all);
+                l_all += w * base[r * stride_r + D + 1];
+                o += w * base[r * stride_r + d];
+            }
+        }
+        out[static_cast<size_t>(bh) * D + d] = Elt<T>::from_float(l_all > 0.f ? o / l_all : 0.f);
+    }
+}
+
+}  // namespace b2kv
+
+extern "C" int b2kv_decode_partial(const void* q, const void* k_cache, const void* v_cache, float* partial_out,
+                                   const int32_t* seq_lens, int len, int len_bias, int B, int H, int D, int T_upper,
+                                   int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype, void* workspace,
+                                   size_t workspace_bytes, int32_t* dev_status, void* stream) {
+    if (!partial_out || !aligned16(partial_out)) return partial_out ? B2KV_ERR_ALIGN : B2KV_ERR_BAD_ARG;
+    GatherInfo none{};
+    return decode_entry(q, k_cache, v_cache, partial_out, seq_lens, len, len_bias, nullptr, 0, 0, 0, B, H, D, T_upper,
+                        stride_b, stride_t, stride_h, dtype, workspace, workspace_bytes, dev_status, stream, &none,
+                        partial_out);
+}
+
+extern "C" int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* out, int dtype, void* stream) {
+    if (!parts || !out || R <= 0 || B <= 0 || H <= 0 || D <= 0) return B2KV_ERR_BAD_ARG;
+    if (elt_bytes(dtype) == 0) return B2KV_ERR_UNSUPPORTED;
+    const int threads = D < 32 ? 32 : (D > 256 ? 256 : D);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == B2KV_DTYPE_F32)
+        merge_partials_kernel<float><<<B * H, threads, 0, s>>>(parts, R, B * H, D, static_cast<float*>(out));
+    else
+        merge_partials_kernel<__nv_bfloat16><<<B * H, threads, 0, s>>>(parts, R, B * H, D, static_cast<__nv_bfloat16*>(out));
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
 
 extern "C" int b2kv_decode_allgather(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
                                      int len, int len_bias, int B, int H_local, int D, int T_upper, int64_t stride_b,

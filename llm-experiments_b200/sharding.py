@@ -152,3 +152,60 @@ class FusedHeadGather:
             self.world, self.H_total, self.epoch, dev_status_ptr(ctx), stream)
         _native.check(rc)
         return self.out[buf]
+
+
+# ------------------------------------------------------------------------------------------
+# sequence split (context parallel): every rank holds a slice of each sequence's tokens
+# ------------------------------------------------------------------------------------------
+
+
+def decode_partial(ctx, cache, layer_idx: int, q_new) -> torch.Tensor:
+    """Attention of ``q_new [B, H*D]`` over THIS rank's slice of the cache, left unnormalised:
+    returns float32 ``[B*H, D + 2]`` (row sums, then the maximum in the log2 domain - ``-inf`` when
+    the slice holds no token of that sequence - then the sum of weights), ready for ``merge_partials``."""
+    from . import _native
+    from .batch import batch_op_begin, dev_status_ptr
+    from .kv_cache import cache_strides, decode_workspace, dtype_code
+
+    if cache.block_table is not None:
+        raise ValueError("the sequence-split decode takes contiguous caches")
+    B, H, D = cache.batch_size, cache.n_heads, cache.head_dim
+    part = torch.empty((B * H, D + 2), dtype=torch.float32, device=q_new.buffer.device)
+    ws = decode_workspace(cache)
+    stream = batch_op_begin(ctx)
+    s0, st, sh = cache_strides(cache)
+    layer = cache.layers[layer_idx]
+    t_upper = max(1, min(cache.current_len, cache.max_seq_len))
+    rc = _native.lib.b2kv_decode_partial(
+        q_new.buffer.data_ptr(), layer.k_cache.buffer.data_ptr(), layer.v_cache.buffer.data_ptr(), part.data_ptr(),
+        None if cache.seq_lens is None else cache.seq_lens.data_ptr(), cache.current_len, 0, B, H, D, t_upper, s0, st,
+        sh, dtype_code(cache.dtype), ws.data_ptr(), ws.numel(), dev_status_ptr(ctx), stream)
+    _native.check(rc)
+    return part
+
+
+def merge_partials(ctx, parts: torch.Tensor, batch: int, n_heads: int, head_dim: int, dtype: torch.dtype) -> torch.Tensor:
+    """Combines ``parts [R, B*H, D + 2]`` (one ``decode_partial`` result per slice) into ``[B, H*D]``."""
+    from . import _native
+    from .batch import batch_op_begin
+    from .kv_cache import dtype_code
+
+    parts = parts.contiguous()
+    R = parts.shape[0]
+    out = torch.empty((batch, n_heads * head_dim), dtype=dtype, device=parts.device)
+    stream = batch_op_begin(ctx)
+    _native.check(_native.lib.b2kv_merge_partials(parts.data_ptr(), R, batch, n_heads, head_dim, out.data_ptr(),
+                                                  dtype_code(dtype), stream))
+    return out
+
+
+def sequence_split_decode(ctx, cache, layer_idx: int, q_new, group=None) -> torch.Tensor:
+    """Decode step when each rank caches a different slice of every sequence's tokens (all heads):
+    local unnormalised attention, one all-gather of the ``[B*H, D + 2]`` float partials, merge.
+    Returns the full ``[B, H*D]`` output on every rank."""
+    world = dist.get_world_size(group)
+    part = decode_partial(ctx, cache, layer_idx, q_new)
+    gathered = torch.empty((world * part.shape[0], part.shape[1]), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(gathered, part, group=group)
+    return merge_partials(ctx, gathered.reshape(world, part.shape[0], part.shape[1]), cache.batch_size, cache.n_heads,
+                          cache.head_dim, cache.dtype)

@@ -64,6 +64,21 @@ def _worker(rank, world, port, out_dir):
             np.testing.assert_allclose(U.to_f32(via_nccl), want, **U.TOL[dtype])
             assert torch.equal(via_fused.view(torch.uint8), via_nccl.view(torch.uint8))
             assert int(ctx.dev_status.item()) == 0
+        # sequence split: rank r caches tokens [r*T/W, (r+1)*T/W) of every sequence, all heads
+        per = T_max // world
+        lo = rank * per
+        local_lens = [max(0, min(n, lo + per) - lo) for n in lens]
+        seq_cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=per, n_layers=1, n_heads=H,
+                                                               head_dim=D, dtype=dtype, layout="bhtd", ragged=True))
+        U.fill_cache_logical(seq_cache, 0, k_log[:, lo:lo + per].contiguous(), v_log[:, lo:lo + per].contiguous())
+        gpu.kv_cache_set_lengths(seq_cache, local_lens)
+        seq_cache.current_len = max(1, seq_cache.current_len)
+        q = torch.randn((B, H * D), generator=g).to(dtype).to(dev)
+        gpu.batch_begin(ctx)
+        via_seq = sharding.sequence_split_decode(ctx, seq_cache, 0, U.buf2d(pkg, ctx, q))
+        gpu.batch_commit(ctx)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(U.to_f32(via_seq), U.oracle_decode(q, k_log, v_log, lens), **U.TOL[dtype])
         open(os.path.join(out_dir, f"ok_{rank}"), "w").write("ok")
         dist.barrier()
     finally:
