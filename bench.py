@@ -577,7 +577,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fused-gather", action="store_true",
                     help="head-split workloads: gather the outputs with peer stores from the merge kernel instead of NCCL")
+    ap.add_argument("--tune", action="append", default=[], metavar="NAME=VALUE",
+                    help="set a kernel tuning knob of the library (b2kv_tune), e.g. prefill_variant=1")
     args = ap.parse_args()
+    if args.tune and args.impl != "reference":
+        import __graft_entry__
+
+        native = __graft_entry__.import_package()._native
+        for item in args.tune:
+            name, _, value = item.partition("=")
+            native.tune(name, int(value))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     w = WORKLOADS[args.workload]

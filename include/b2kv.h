@@ -214,7 +214,8 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
 /*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
- * "prefill_force_simt"); returns B2KV_ERR_BAD_ARG
+ * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,
+ * N a multiple of 256); returns B2KV_ERR_BAD_ARG
  * for an unknown name.  Defaults are chosen per shape when a knob is 0.  No counterpart in
  * the reference beyond the tile-size fields of GPUConfig (gpu_types.py:69-121).
  */

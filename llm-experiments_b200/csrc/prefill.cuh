@@ -23,5 +23,7 @@ struct PrefillParams {
 int prefill_simt(const PrefillParams& p, int D, int dtype, void* stream);
 // Tensor-core kernel: returns B2KV_ERR_UNSUPPORTED when the shape is not one it takes.
 int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream);
+// Tensor-core kernel on CTA pairs (bf16, head_dim 128, N a multiple of 256): same contract.
+int prefill_tensor_core_pair(const PrefillParams& p, int D, int dtype, void* stream);
 
 }  // namespace b2kv

@@ -238,7 +238,11 @@ extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O
     PrefillParams p{Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, B, N, H,
                     static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D)))};
     if (!tune_get("prefill_force_simt")) {
-        int rc = prefill_tensor_core(p, D, dtype, stream);
+        // "prefill_variant": 0 = one-CTA tensor-core kernel (default), 2 = CTA-pair kernel where its
+        // shape limits allow
+        int rc = B2KV_ERR_UNSUPPORTED;
+        if (tune_get("prefill_variant") == 2) rc = prefill_tensor_core_pair(p, D, dtype, stream);
+        if (rc == B2KV_ERR_UNSUPPORTED) rc = prefill_tensor_core(p, D, dtype, stream);
         if (rc != B2KV_ERR_UNSUPPORTED) return rc;
     }
     return prefill_simt(p, D, dtype, stream);

@@ -85,3 +85,40 @@ def test_prefill_writes_cache_rows_bit_exact_then_decode_continues(pkg, ctx, dty
     tol = U.TOL[dtype]
     np.testing.assert_allclose(U.to_f32(out), U.to_f32(O.reshape(B, N, E)[:, N - 1]), rtol=max(tol["rtol"], 1e-4),
                                atol=tol["atol"])
+
+
+@pytest.mark.parametrize("B,N,H,with_cache", [(1, 256, 1, False), (2, 512, 3, True), (1, 1280, 2, True), (2, 2048, 2, False)])
+def test_prefill_cta_pair_kernel_vs_oracle_and_one_cta_kernel(pkg, ctx, B, N, H, with_cache):
+    """The CTA-pair kernel (opt-in through the "prefill_variant" knob) against the oracle and against
+    the default kernel: O within the bf16 tolerance, L / M as the shader defines them, cache rows bit-exact."""
+    gpu = pkg.gpu
+    D, dtype = 128, torch.bfloat16
+    E = H * D
+    Q = U.randn((B, N, E), dtype, ctx.device, 21)
+    K = U.randn((B, N, E), dtype, ctx.device, 22)
+    V = U.randn((B, N, E), dtype, ctx.device, 23)
+    results = {}
+    try:
+        for variant in (0, 2):
+            pkg._native.tune("prefill_variant", variant)
+            cache = None
+            if with_cache:
+                cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=N + 64, n_layers=1, n_heads=H,
+                                                                   head_dim=D, dtype=dtype, layout="bhtd"))
+            O, Lb, Mb = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, cache=cache)
+            results[variant] = (O.clone(), Lb.clone(), Mb.clone(), cache)
+    finally:
+        pkg._native.tune("prefill_variant", 0)
+    flat = lambda a: U.to_oracle(a.reshape(B * N, E))  # noqa: E731
+    Ow, Lw, Mw = c_oracle.prefill(flat(Q), flat(K), flat(V), B, N, H, D)
+    O2, L2, M2, cache2 = results[2]
+    np.testing.assert_allclose(U.to_f32(O2), Ow, **U.TOL[dtype])
+    np.testing.assert_allclose(L2.cpu().numpy(), Lw, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(M2.cpu().numpy(), Mw, rtol=1e-4, atol=1e-5)
+    O0 = results[0][0]
+    assert float((O2.float() - O0.float()).abs().max()) <= 2e-2
+    if with_cache:
+        kview = U.logical_view(cache2, cache2.layers[0], "k")
+        vview = U.logical_view(cache2, cache2.layers[0], "v")
+        assert torch.equal(kview[:, :N].reshape(B, N, E), K) and torch.equal(vview[:, :N].reshape(B, N, E), V)
+        assert float(kview[:, N:].float().abs().sum()) == 0.0
