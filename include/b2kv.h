@@ -212,6 +212,26 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
                  int D, int dtype, void* stream);
 
 /*
+ * The tail of a cached generation step, fp32 like the reference's buffers.  Each replaces one
+ * dispatch of simple-llm/src/gpu/gpu_pass_forward.py:
+ *   b2kv_layernorm            layernorm :140-176 (WGSL src/gpu/gpu_kernels.py:137-249): per row of
+ *                             [n_rows, size], (x - mean) / sqrt(var + epsilon) * gamma + beta, var = mean
+ *                             of (x - mean)^2; epsilon is GPUConfig.layernorm_epsilon (gpu_types.py:197).
+ *   b2kv_extract_last_tokens  extract_last_tokens :285-328 (WGSL :839-887): row b*seq_len + seq_len - 1
+ *                             of [batch_size*seq_len, embedding_dim] to row b of [batch_size, embedding_dim].
+ *   b2kv_softmax              softmax :462-494 (WGSL :890-992): exp(x - max) / sum over each row.
+ *   b2kv_argmax               greedy choice of the next token, int32 index per row (lowest index among
+ *                             equal maxima); the reference does this on the host after reading the
+ *                             probabilities back (src/generate.py).
+ * Pointers are device pointers, 16-byte aligned; the calls are asynchronous on `stream`.
+ */
+int b2kv_layernorm(const float* x, const float* gamma, const float* beta, float* out, int64_t n_rows, int size,
+                   float epsilon, void* stream);
+int b2kv_extract_last_tokens(const float* in, float* out, int batch_size, int seq_len, int embedding_dim, void* stream);
+int b2kv_softmax(const float* logits, float* probs, int64_t n_rows, int size, void* stream);
+int b2kv_argmax(const float* x, int32_t* out, int n_rows, int size, void* stream);
+
+/*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,

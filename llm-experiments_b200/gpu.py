@@ -1,5 +1,5 @@
 """Facade with the reference's names (simple-llm/src/gpu/gpu.py:82-156), restricted to the
-KV-cache attention path: callers write ``from <package> import gpu`` and use
+KV-cache attention path and the tail of a generation step: callers write ``from <package> import gpu`` and use
 ``gpu.kv_cache_update(ctx, ...)`` exactly as with the reference's ``gpu`` module."""
 from .attention import flash_attention
 from .batch import batch_begin, batch_commit
@@ -21,6 +21,7 @@ from .kv_cache import (
     kv_cache_set_lengths,
     kv_cache_update,
 )
+from .step_tail import argmax, extract_last_tokens, layernorm, softmax
 from .types import GPUBuffer1D, GPUBuffer2D, GPUConfig, GPUContext, KVCache, KVCacheConfig, KVCacheLayer
 
 __all__ = [
@@ -32,4 +33,5 @@ __all__ = [
     "batch_begin", "batch_commit",
     "kv_cache_create", "kv_cache_reset", "kv_cache_update", "attention_with_kv_cache",
     "kv_cache_gather", "kv_cache_set_lengths",
+    "layernorm", "extract_last_tokens", "softmax", "argmax",
 ]

@@ -32,6 +32,7 @@ class GPUConfig:
     attention_workgroup_size: int = 256
     max_workgroups_per_dim: int = 65535
     max_batch_operations: int = 1000
+    layernorm_epsilon: float = 1e-5
     # ---- extensions ----
     enforce_reference_decode_limit: bool = False
     """True: refuse current_len > attention_workgroup_size as the reference does

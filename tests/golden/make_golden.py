@@ -8,6 +8,8 @@ jax and wgpu at the top), so this script reads it as text and executes only the
 reference-math lines, straight from the reference tree, on the recipes' inputs:
 
 * lines 2328-2367: the numpy loop that computes the expected decode-attention output;
+* lines 543-552, 1681-1686, 2082-2083: the expected outputs of the layernorm, softmax and
+  extract_last_tokens tests (the first GOLDEN_ROWS rows of each are stored);
 * lines 776-810:   the dense causal attention of the flash test.  It is written with
   ``jax.numpy``; every call it makes (array, reshape, transpose, sqrt, einsum, tril,
   ones, where) exists in numpy with the same meaning, so ``jnp`` is bound to numpy
@@ -34,7 +36,7 @@ import numpy as np
 HERE = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
 
-from oracle import kv_oracle  # noqa: E402  (recipe inputs only)
+from oracle import kv_oracle, step_tail_oracle  # noqa: E402  (recipe inputs only)
 
 
 def snippet(lines, first, last):
@@ -102,6 +104,27 @@ def main():
         exec(compile(snippet(lines, 776, 810), str(test_file), "exec"), ns)
         out[f"flash_out_{i}"] = np.asarray(ns["output_jax_np"], dtype=np.float32)
         out[f"flash_in_checksum_{i}"] = np.array([float(Q_np.sum()), float(K_np.sum()), float(V_np.sum())])
+
+    # ---- tail of a generation step: layernorm, softmax, extract_last_tokens ----
+    assert "x_jax = jnp.array(x_np)" in lines[542] and "y_jax_np = np.array(y_jax)" in lines[551], lines[542]
+    assert "softmax_jax_list = []" in lines[1680] and "softmax_jax_np = np.array(softmax_jax_list)" in lines[1685]
+    assert "input_reshaped = input_np.reshape" in lines[2081] and "expected_np = input_reshaped" in lines[2082]
+    rows = step_tail_oracle.GOLDEN_ROWS
+    for i, (n_elements, size) in enumerate(step_tail_oracle.LAYERNORM_RECIPE_SHAPES):
+        x_np, gamma_np, beta_np = step_tail_oracle.recipe_layernorm_inputs(n_elements, size)
+        ns = {"np": np, "jnp": np, "x_np": x_np, "gamma_np": gamma_np, "beta_np": beta_np}
+        exec(compile(snippet(lines, 543, 552), str(test_file), "exec"), ns)
+        out[f"layernorm_out_{i}"] = np.asarray(ns["y_jax_np"], dtype=np.float32)[:rows]
+    for i, (batch_size, vocab_size, transform) in enumerate(step_tail_oracle.SOFTMAX_RECIPES):
+        x_np = step_tail_oracle.recipe_softmax_inputs(batch_size, vocab_size, transform)
+        ns = {"np": np, "jnp": np, "jax": jax_shim, "x_np": x_np, "batch_size": batch_size}
+        exec(compile(snippet(lines, 1681, 1686), str(test_file), "exec"), ns)
+        out[f"softmax_out_{i}"] = np.asarray(ns["softmax_jax_np"], dtype=np.float32)[:rows]
+    for i, (batch_size, seq_len, emb_dim) in enumerate(step_tail_oracle.EXTRACT_RECIPE_SHAPES):
+        input_np = step_tail_oracle.recipe_extract_inputs(batch_size, seq_len, emb_dim)
+        ns = {"np": np, "input_np": input_np, "batch_size": batch_size, "seq_len": seq_len, "emb_dim": emb_dim}
+        exec(compile(snippet(lines, 2082, 2083), str(test_file), "exec"), ns)
+        out[f"extract_out_{i}"] = np.asarray(ns["expected_np"], dtype=np.float32)[:rows]
 
     np.savez_compressed(HERE / "reference_recipes.npz", **out)
     print("wrote", HERE / "reference_recipes.npz")

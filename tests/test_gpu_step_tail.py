@@ -1,0 +1,112 @@
+"""GPU parity of the generation-step tail (layernorm, softmax, extract_last_tokens, argmax): the
+reference's seeded test recipes through the operator mirrors against the fixture and the oracle, plus
+row lengths that take every code path of the kernels."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import step_tail_oracle as T
+from tests import kv_util as U
+
+pytestmark = pytest.mark.gpu
+ROWS = T.GOLDEN_ROWS
+
+
+@pytest.fixture(scope="module")
+def ctx(pkg):
+    return U.make_ctx(pkg)
+
+
+def _dev(ctx, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(ctx.device)
+
+
+def _layernorm(pkg, ctx, x, gamma, beta):
+    gpu = pkg.gpu
+    n, size = x.shape
+    out = gpu.gpu_buffer_2d_create(ctx, n, size)
+    gpu.batch_begin(ctx)
+    gpu.layernorm(ctx, gpu.gpu_buffer_2d_create(ctx, n, size, _dev(ctx, x)), gpu.gpu_buffer_1d_create(ctx, size, _dev(ctx, gamma)),
+                  gpu.gpu_buffer_1d_create(ctx, size, _dev(ctx, beta)), out)
+    gpu.batch_commit(ctx)
+    return out.buffer.cpu().numpy()
+
+
+def _softmax(pkg, ctx, x):
+    gpu = pkg.gpu
+    b, v = x.shape
+    out = gpu.gpu_buffer_2d_create(ctx, b, v)
+    gpu.batch_begin(ctx)
+    gpu.softmax(ctx, gpu.gpu_buffer_2d_create(ctx, b, v, _dev(ctx, x)), out)
+    gpu.batch_commit(ctx)
+    return out.buffer.cpu().numpy()
+
+
+@pytest.mark.parametrize("case", range(len(T.LAYERNORM_RECIPE_SHAPES)))
+def test_layernorm_reference_recipes(pkg, ctx, golden, case):
+    n, size = T.LAYERNORM_RECIPE_SHAPES[case]
+    x, gamma, beta = T.recipe_layernorm_inputs(n, size)
+    out = _layernorm(pkg, ctx, x, gamma, beta)
+    np.testing.assert_allclose(out[:ROWS], golden[f"layernorm_out_{case}"], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(out, T.layernorm(x, gamma, beta), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("case", range(len(T.SOFTMAX_RECIPES)))
+def test_softmax_reference_recipes(pkg, ctx, golden, case):
+    b, v, transform = T.SOFTMAX_RECIPES[case]
+    x = T.recipe_softmax_inputs(b, v, transform)
+    out = _softmax(pkg, ctx, x)
+    np.testing.assert_allclose(out[:ROWS], golden[f"softmax_out_{case}"], rtol=1e-4, atol=1e-7)
+    np.testing.assert_allclose(out.sum(axis=1), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("case", range(len(T.EXTRACT_RECIPE_SHAPES)))
+def test_extract_last_tokens_reference_recipes(pkg, ctx, golden, case):
+    gpu = pkg.gpu
+    b, s, e = T.EXTRACT_RECIPE_SHAPES[case]
+    x = T.recipe_extract_inputs(b, s, e)
+    out = gpu.gpu_buffer_2d_create(ctx, b, e)
+    gpu.batch_begin(ctx)
+    gpu.extract_last_tokens(ctx, gpu.gpu_buffer_2d_create(ctx, b * s, e, _dev(ctx, x)), out, b, s, e)
+    gpu.batch_commit(ctx)
+    got = out.buffer.cpu().numpy()
+    assert np.array_equal(got[:ROWS], golden[f"extract_out_{case}"])
+    assert np.array_equal(got, T.extract_last_tokens(x, b, s, e))
+
+
+# row lengths: below one warp's vector width, not a multiple of 4 (scalar path), each threads-per-row
+# class, the largest row kept in registers, and rows that are re-read instead
+@pytest.mark.parametrize("n,size", [(3, 1), (5, 7), (9, 33), (4, 252), (6, 260), (7, 1028), (64, 4096), (3, 8192),
+                                    (2, 8196), (2, 10001), (300, 64)])
+def test_layernorm_and_softmax_row_lengths_vs_oracle(pkg, ctx, n, size):
+    rng = np.random.default_rng(size)
+    x = (rng.standard_normal((n, size)) * 3 + 1).astype(np.float32)
+    gamma = rng.standard_normal(size).astype(np.float32)
+    beta = rng.standard_normal(size).astype(np.float32)
+    np.testing.assert_allclose(_layernorm(pkg, ctx, x, gamma, beta), T.layernorm(x, gamma, beta), rtol=1e-4, atol=2e-5)
+    np.testing.assert_allclose(_softmax(pkg, ctx, x), T.softmax(x), rtol=1e-4, atol=1e-8)
+
+
+@pytest.mark.parametrize("b,s,e", [(3, 5, 6), (2, 7, 1), (64, 1, 4096)])
+def test_extract_last_tokens_odd_shapes(pkg, ctx, b, s, e):
+    gpu = pkg.gpu
+    x = np.random.default_rng(e).standard_normal((b * s, e)).astype(np.float32)
+    out = gpu.gpu_buffer_2d_create(ctx, b, e)
+    gpu.batch_begin(ctx)
+    gpu.extract_last_tokens(ctx, gpu.gpu_buffer_2d_create(ctx, b * s, e, _dev(ctx, x)), out, b, s, e)
+    gpu.batch_commit(ctx)
+    assert np.array_equal(out.buffer.cpu().numpy(), T.extract_last_tokens(x, b, s, e))
+
+
+def test_argmax_takes_the_lowest_index_among_equals(pkg, ctx):
+    gpu = pkg.gpu
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((37, 50257)).astype(np.float32)
+    x[1, 40000] = x[1, 123] = 9.0   # tie: the lower index wins
+    x[2, :] = -2.0                  # all equal: index 0
+    x[3, 50256] = 11.0              # last element
+    idx = gpu.gpu_buffer_1d_create(ctx, 37, dtype=torch.int32)
+    gpu.batch_begin(ctx)
+    gpu.argmax(ctx, gpu.gpu_buffer_2d_create(ctx, 37, 50257, _dev(ctx, x)), idx)
+    gpu.batch_commit(ctx)
+    assert np.array_equal(idx.buffer.cpu().numpy(), T.argmax(x))
