@@ -51,6 +51,8 @@ WORKLOADS = {
     "longctx_headsplit": dict(B=4, H=64, D=128, lo=131072, hi=131072, block_size=0, head_split=True,
                               desc="long-context decode: B=4 H=64 D=128 bf16, len 131072, heads split over the "
                                    "GPUs, outputs all-gathered with NCCL"),
+    "qkv_append": dict(B=64, H=32, D=128, T=256, layers=4, qkv=True,
+                       desc="Q/K/V projection fused with the cache append: B=64 E=4096 (H=32 D=128) bf16, one layer per step"),
     "prefill_small": dict(B=2, H=32, D=128, N=4096, prefill=True,
                           desc="causal prefill cut to 2 sequences (for profiler captures)"),
     "prefill": dict(B=8, H=32, D=128, N=4096, prefill=True,
@@ -196,7 +198,7 @@ def cpu_port_run(w, lens, steps, warmup, sample_seqs, log=None):
 def run_reference(args, w, rank):
     if rank != 0:
         return
-    if w.get("prefill"):
+    if w.get("prefill") or w.get("qkv"):
         w = WORKLOADS["decode"]  # the CPU arm times the decode step, the headline workload
     lens = make_lengths(w, 0)
     steps = max(1, args.steps)
@@ -560,6 +562,123 @@ def run_prefill(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_qkv_append(args, w, rank, world):
+    """One decode step's Q/K/V projection fused with the cache append; value = tokens/s, roofline = HBM
+    (the step streams 3*E*E weights).  The layers' weights (4 x 100 MB) are used in turn, so that a step's
+    weights are not in L2 from the step before."""
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pkg = __graft_entry__.import_package()
+    gpu = pkg.gpu
+    ctx = gpu.context_create(local_rank)
+    B, H, D, T, n_layers = w["B"], w["H"], w["D"], w["T"], w["layers"]
+    E = H * D
+    dtype = torch.bfloat16
+    gen = torch.Generator(device=device).manual_seed(3000 + rank)
+    rnd = lambda shape, scale: (torch.randn(shape, generator=gen, device=device) * scale).to(dtype)  # noqa: E731
+    wrap = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    weights = [[wrap(rnd((E, E), E ** -0.5)) for _ in range(3)] for _ in range(n_layers)]
+    x, q = rnd((B, E), 1.0), torch.empty((B, E), dtype=dtype, device=device)
+    xb, qb = wrap(x), wrap(q)
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T, n_layers=n_layers, n_heads=H,
+                                                       head_dim=D, dtype=dtype, layout="bhtd", ragged=True))
+    lens = np.random.default_rng(0).integers(0, T - 1, size=B).astype(np.int32)
+    gpu.kv_cache_set_lengths(cache, lens)
+    state = {"i": 0}
+
+    def step_device():
+        li = state["i"] % n_layers
+        state["i"] += 1
+        gpu.batch_begin(ctx)
+        gpu.qkv_project_append(ctx, cache, li, xb, *weights[li], qb, advance=False)
+        gpu.batch_commit(ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    steps, warm = args.steps, max(3, args.warmup)
+    for _ in range(warm):
+        step_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ms_step = timed(step_device, steps) / steps
+    xh, qh = x.cpu().pin_memory(), torch.empty_like(q, device="cpu").pin_memory()
+
+    def step_e2e():
+        gpu.gpu_buffer_2d_write(ctx, xh, xb)
+        step_device()
+        gpu.gpu_buffer_2d_read(ctx, qb, qh)
+
+    step_e2e()
+    ms_e2e = timed(step_e2e, steps) / steps
+    clocks = sampler.finish()
+    es = 2
+    bytes_step = 3 * E * E * es + B * E * es + 3 * B * E * es
+    peak, kind = measured_hbm_peak()
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import kv_oracle
+
+        f32 = lambda t: t.float().cpu().numpy()  # noqa: E731
+        xs, ws = f32(x), [f32(t.buffer) for t in weights[0]]
+        reps = 3
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            kv_oracle.qkv_project(xs, *ws)
+        dt = (time.perf_counter() - t0) / reps
+        cpu = {"value": B / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+               "sample": f"the three projections of one step in float64 numpy ({dt:.2f} s per step)"}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "projected tokens/s (one layer's Q/K/V projection + cache append per step)",
+        "value": world * B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
+                   "l2": f"{n_layers} layers' weights ({n_layers * 3 * E * E * es / 1e6:.0f} MB) used in turn, larger than L2",
+                   "parallelism": f"batch-sharded x{world}, no collective"},
+        "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": B * E * es, "d2h_bytes_per_step": B * E * es},
+        "gpu_launches": steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "qkv_append_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": kind, "algorithmic_bytes_per_launch": bytes_step,
+                     "traffic": None},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of the split kernel per attended (token, head), from
 # an ncu capture of the 8-sequence case (`--workload decode_small`: 412.4 MB for
 # 24908 tokens x 32 heads; the algorithmic figure is 512 B).  Traffic grows in proportion to the
@@ -593,6 +712,9 @@ def main():
     w.setdefault("block_size", 0)
     if w.get("prefill") and args.impl != "reference":
         run_prefill(args, w, rank, world)
+        return
+    if w.get("qkv") and args.impl != "reference":
+        run_qkv_append(args, w, rank, world)
         return
     if args.impl == "reference":
         run_reference(args, w, rank)

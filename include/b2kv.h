@@ -232,6 +232,21 @@ int b2kv_softmax(const float* logits, float* probs, int64_t n_rows, int size, vo
 int b2kv_argmax(const float* x, int32_t* out, int n_rows, int size, void* stream);
 
 /*
+ * Q / K / V projection of one decode step fused with the cache append (bf16 storage, fp32 accumulate).
+ * Replaces, for the rows of one decode step, the three matmul dispatches of the attention block
+ * (simple-llm/src/wgpu_backend.py:812-831; gpu_pass_forward.py:35-82, C = A @ B) followed by
+ * kv_cache_update (gpu_kv_cache.py:113-186):
+ *   q_out[b, :]                = x[b, :] @ wq
+ *   k_cache row (b, position)  = x[b, :] @ wk      (same for v_cache with wv)
+ * x is [B, E], the weights are [E, E] row-major ([in, out], as the reference stores them), q_out is
+ * [B, E]; position = seq_pos[b] when seq_pos is non-NULL, else `pos`; the cache is addressed with the
+ * strides of b2kv_append.  E = H * D, E a multiple of 128, B <= 128.  The lengths are not advanced.
+ */
+int b2kv_qkv_append(const void* x, const void* wq, const void* wk, const void* wv, void* q_out, void* k_cache,
+                    void* v_cache, const int32_t* seq_pos, int pos, int B, int E, int H, int D, int T_max,
+                    int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
+
+/*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,

@@ -1,0 +1,52 @@
+"""Q / K / V projection of one decode step fused with the KV-cache append.
+
+The reference's attention block runs three ``matmul`` dispatches on the normalised hidden state
+(simple-llm/src/wgpu_backend.py:812-831; ``matmul(ctx, A, B, C)`` of
+src/gpu/gpu_pass_forward.py:35-82 computes C = A @ B) and a cached decode would follow them with
+``kv_cache_update`` (src/gpu/gpu_kv_cache.py:113-186).  ``qkv_project_append`` does the four steps in
+one kernel for the rows of a decode step: Q goes to its buffer, the new K / V rows go straight into
+the cache.  Checks and texts follow ``kv_cache_update``; bf16 caches with a contiguous layout only
+(other cases: project with matmuls, then ``kv_cache_update``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+from .batch import batch_op_begin, dev_status_ptr, validate_buffer_shape_2d
+from .kv_cache import _ptr, cache_strides, dtype_code
+from .types import GPUBuffer2D, GPUContext, KVCache
+
+
+def qkv_project_append(ctx: GPUContext, cache: KVCache, layer_idx: int, x: GPUBuffer2D, wq: GPUBuffer2D,
+                       wk: GPUBuffer2D, wv: GPUBuffer2D, q_out: GPUBuffer2D, advance: bool = True) -> None:
+    """``q_out = x @ wq``; row ``current_len`` (or ``seq_lens[b]``) of the layer's K / V cache
+    ``= x @ wk`` / ``x @ wv``; then, like ``kv_cache_update``, the length advances by one."""
+    if layer_idx < 0 or layer_idx >= len(cache.layers):
+        raise ValueError(f"layer_idx {layer_idx} out of range [0, {len(cache.layers)})")
+    if cache.current_len >= cache.max_seq_len:
+        raise ValueError(f"Cache is full: current_len={cache.current_len}, max_seq_len={cache.max_seq_len}")
+    embedding_dim = cache.n_heads * cache.head_dim
+    validate_buffer_shape_2d(x, (cache.batch_size, embedding_dim), "x")
+    validate_buffer_shape_2d(q_out, (cache.batch_size, embedding_dim), "q_out")
+    for name, w in (("wq", wq), ("wk", wk), ("wv", wv)):
+        validate_buffer_shape_2d(w, (embedding_dim, embedding_dim), name)
+    if cache.dtype != torch.bfloat16 or any(t.buffer.dtype != torch.bfloat16 for t in (x, wq, wk, wv, q_out)):
+        raise ValueError("qkv_project_append takes bfloat16 buffers and a bfloat16 cache")
+    if cache.block_table is not None:
+        raise ValueError("qkv_project_append does not take a paged cache; project, then kv_cache_update")
+    if cache.batch_size > 128 or embedding_dim % 128 != 0:
+        raise ValueError("qkv_project_append needs batch_size <= 128 and an embedding_dim that is a multiple of 128")
+    layer = cache.layers[layer_idx]
+    s0, st, sh = cache_strides(cache)
+    stream = batch_op_begin(ctx)
+    rc = _native.lib.b2kv_qkv_append(x.buffer.data_ptr(), wq.buffer.data_ptr(), wk.buffer.data_ptr(), wv.buffer.data_ptr(),
+                                     q_out.buffer.data_ptr(), layer.k_cache.buffer.data_ptr(),
+                                     layer.v_cache.buffer.data_ptr(), _ptr(cache.seq_lens), cache.current_len,
+                                     cache.batch_size, embedding_dim, cache.n_heads, cache.head_dim, cache.max_seq_len,
+                                     s0, st, sh, dtype_code(cache.dtype), dev_status_ptr(ctx), stream)
+    _native.check(rc)
+    if advance:
+        if cache.seq_lens is not None:
+            cache.seq_lens.add_(1)  # stream-ordered after the kernel, which read the old positions
+        cache.current_len += 1

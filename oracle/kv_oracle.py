@@ -272,3 +272,11 @@ def recipe_flash_inputs(batch, seq_len, n_heads, head_dim, seed=42):
     K = np.random.randn(*shape).astype(np.float32)
     V = np.random.randn(*shape).astype(np.float32)
     return Q, K, V
+
+
+def qkv_project(x, wq, wk, wv):
+    """The three projections of the attention block, C = A @ B per weight matrix
+    (simple-llm/src/wgpu_backend.py:812-831, gpu_pass_forward.py:35-82), accumulated in float64 from
+    the given (already storage-rounded) inputs.  Returns float32 arrays [rows, E]."""
+    x64 = np.asarray(x, dtype=np.float64)
+    return tuple((x64 @ np.asarray(w, dtype=np.float64)).astype(np.float32) for w in (wq, wk, wv))

@@ -1,0 +1,91 @@
+"""The Q / K / V projection fused with the cache append against the oracle (three matmuls, then the
+append indexing of the reference): Q and the new cache rows within two bf16 units in the last place
+of the float64-accumulated product (rtol 2^-7, plus atol 1e-2 for values near zero), every other cache row
+untouched bit for bit, and a decode over the updated cache equal to the oracle's."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle, kv_oracle
+from tests import kv_util as U
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2.0 ** -7, 1e-2
+
+
+@pytest.fixture(scope="module")
+def ctx(pkg):
+    return U.make_ctx(pkg)
+
+
+def _bf16(ctx, shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(ctx.device)
+
+
+@pytest.mark.parametrize("B,H,D,layout,ragged", [(3, 2, 64, "bthd", False), (17, 4, 64, "bhtd", True),
+                                                  (64, 8, 128, "bhtd", True), (128, 2, 128, "bthd", True),
+                                                  (1, 1, 128, "bhtd", False)])
+def test_qkv_project_append_vs_oracle(pkg, ctx, B, H, D, layout, ragged):
+    gpu = pkg.gpu
+    E, T_max = H * D, 40
+    x = _bf16(ctx, (B, E), 1)
+    wq, wk, wv = (_bf16(ctx, (E, E), s, scale=E ** -0.5) for s in (2, 3, 4))
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=2, n_heads=H, head_dim=D,
+                                                       dtype=torch.bfloat16, layout=layout, ragged=ragged))
+    # pre-fill the layer with known rows, then pick where the step writes
+    for layer in cache.layers:
+        layer.k_cache.buffer.copy_(_bf16(ctx, tuple(layer.k_cache.buffer.shape), 5))
+        layer.v_cache.buffer.copy_(_bf16(ctx, tuple(layer.v_cache.buffer.shape), 6))
+    rng = np.random.default_rng(B)
+    if ragged:
+        lens = rng.integers(0, T_max - 1, size=B).astype(np.int32)
+        gpu.kv_cache_set_lengths(cache, lens)
+    else:
+        lens = np.full(B, 7, dtype=np.int32)
+        cache.current_len = 7
+    before_k = U.logical_view(cache, cache.layers[1], "k").clone()
+    before_v = U.logical_view(cache, cache.layers[1], "v").clone()
+    other_k = cache.layers[0].k_cache.buffer.clone()
+    q_out = torch.zeros((B, E), dtype=torch.bfloat16, device=ctx.device)
+    gpu.batch_begin(ctx)
+    gpu.qkv_project_append(ctx, cache, 1, U.buf2d(pkg, ctx, x), U.buf2d(pkg, ctx, wq), U.buf2d(pkg, ctx, wk),
+                           U.buf2d(pkg, ctx, wv), U.buf2d(pkg, ctx, q_out))
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    want_q, want_k, want_v = kv_oracle.qkv_project(U.to_f32(x), U.to_f32(wq), U.to_f32(wk), U.to_f32(wv))
+    np.testing.assert_allclose(U.to_f32(q_out), want_q, rtol=RTOL, atol=ATOL)
+    after_k = U.logical_view(cache, cache.layers[1], "k")
+    after_v = U.logical_view(cache, cache.layers[1], "v")
+    rows = torch.arange(B)
+    pos = torch.from_numpy(lens.astype(np.int64))
+    np.testing.assert_allclose(U.to_f32(after_k[rows, pos].reshape(B, E)), want_k, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(U.to_f32(after_v[rows, pos].reshape(B, E)), want_v, rtol=RTOL, atol=ATOL)
+    # nothing else moved: restore the written rows and compare bit for bit
+    after_k[rows, pos] = before_k[rows, pos]
+    after_v[rows, pos] = before_v[rows, pos]
+    assert torch.equal(after_k, before_k) and torch.equal(after_v, before_v)
+    assert torch.equal(cache.layers[0].k_cache.buffer, other_k)
+    # lengths advanced like kv_cache_update
+    assert cache.current_len == 8 if not ragged else True
+    if ragged:
+        assert np.array_equal(cache.seq_lens.cpu().numpy(), lens + 1)
+
+
+def test_qkv_project_append_checks(pkg, ctx):
+    gpu = pkg.gpu
+    B, H, D = 2, 2, 64
+    E = H * D
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=4, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=torch.bfloat16, layout="bhtd"))
+    mk = lambda r, c: U.buf2d(pkg, ctx, torch.zeros((r, c), dtype=torch.bfloat16, device=ctx.device))  # noqa: E731
+    x, w, q = mk(B, E), mk(E, E), mk(B, E)
+    gpu.batch_begin(ctx)
+    with pytest.raises(ValueError, match="layer_idx 3 out of range"):
+        gpu.qkv_project_append(ctx, cache, 3, x, w, w, w, q)
+    with pytest.raises(ValueError, match="wk shape mismatch"):
+        gpu.qkv_project_append(ctx, cache, 0, x, w, mk(E, 64), w, q)
+    cache.current_len = 4
+    with pytest.raises(ValueError, match="Cache is full"):
+        gpu.qkv_project_append(ctx, cache, 0, x, w, w, w, q)
+    gpu.batch_commit(ctx)
