@@ -10,7 +10,9 @@
 //   * the product is computed transposed, D[feature, sequence] = W^T x^T, so that the 128 rows of an MMA
 //     are output features (plentiful) and its columns are the sequences (few): one CTA per 128 output
 //     features of Wq | Wk | Wv.  A = a [64 k x 128 features] tile of W, which is an MN-major operand
-//     exactly as the weight matrix lies in memory; B = x, K-major;
+//     exactly as the weight matrix lies in memory; B = x, K-major.  (Handing the weights over transposed,
+//     so that A is K-major too, was measured and is no faster: the kernel is bound by what one SM pulls
+//     from L2 - 32 KB of weights plus 16 KB of x per stage in about 985 clocks - not by the MMAs);
 //   * warp 4 streams the W and x tiles with TMA (128-byte swizzle) through a ring of stages, warp 5
 //     issues tcgen05.mma (M = 128, N = padded batch, K = 16) into one accumulator in tensor memory,
 //     warps 0-3 are the epilogue: thread = output feature = TMEM lane, it reads the sequences' values,
@@ -29,19 +31,25 @@ namespace proj {
 using namespace tc;
 
 constexpr int kFeat = 128;      // output features per CTA (MMA M)
-constexpr int kKTile = 64;      // input features per stage (one 128-byte swizzle span of x)
-constexpr int kStagesP = 6;
-constexpr int kWBytes = kKTile * kFeat * 2;  // 2 feature halves x 64 k x 128 B
-constexpr int kWHalf = kKTile * 128;
+// Input features per stage.  The issuing thread pays about 250 clocks per stage for the barrier wait,
+// the fence and the commit whatever the stage holds, so a stage carries eight MMAs (128 input features),
+// not four.
+constexpr int kKTile = 128;
+constexpr int kMaxStagesP = 6;
+constexpr int kRingBytes = 200 * 1024;  // shared memory given to the ring; as many stages as fit
+constexpr int kWBytes = kKTile * kFeat * 2;  // two halves of 16 KB, see the descriptors below
+constexpr int kWHalf = kWBytes / 2;
 constexpr int kMaxBatch = 128;
 constexpr int kProjThreads = 192;
 
+// Dynamic shared memory holds the ring: `stages` W tiles of 32 KB, then `stages` x tiles (two 64-feature
+// spans of Bn rows each).  A stage takes about 1.5 us from request to arrival, so the bytes in flight
+// decide the streaming rate of an SM: the ring takes all the shared memory there is.
 struct ProjShared {
-    alignas(1024) uint8_t w[kStagesP][kWBytes];
-    alignas(1024) uint8_t x[kStagesP][kMaxBatch * 128];
-    alignas(8) uint64_t full[kStagesP], empty[kStagesP];
+    alignas(8) uint64_t full[kMaxStagesP], empty[kMaxStagesP];
     uint64_t done;
     uint32_t tmem_base;
+    long long row[kMaxBatch];  // element offset of every sequence's output row (-1: outside the cache), computed once
 };
 
 struct ProjParams {
@@ -52,6 +60,7 @@ struct ProjParams {
     int32_t* dev_status;
     int64_t stride_b, stride_t, stride_h;
     int pos, B, Bn, E, H, D, T_max;
+    int stages;
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -71,63 +80,88 @@ __global__ void __launch_bounds__(kProjThreads, 1)
 qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_constant__ CUtensorMap tm_wk,
                   const __grid_constant__ CUtensorMap tm_wv, const __grid_constant__ CUtensorMap tm_x, const ProjParams p) {
     extern __shared__ uint8_t smem_raw[];
-    ProjShared& sm = *reinterpret_cast<ProjShared*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ ProjShared sm;
+    uint8_t* const w_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * kFeat;  // first output feature, in the concatenation Wq | Wk | Wv
     const int which = f0 / p.E;         // 0 = Q, 1 = K, 2 = V
     const int c0 = f0 % p.E;            // first column inside that weight matrix
     const int n_k = p.E / kKTile;
-    const uint32_t stage_bytes = kWBytes + static_cast<uint32_t>(p.Bn) * 128u;
+    const uint32_t x_span = static_cast<uint32_t>(p.Bn) * 128u;  // Bn rows of one 64-feature span
+    uint8_t* const x_ring = w_ring + p.stages * kWBytes;
+    const int n_st = p.stages;
+    const uint32_t stage_bytes = kWBytes + 2 * x_span;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStagesP; ++s) {
+        for (int s = 0; s < kMaxStagesP; ++s) {
             mbar_init(&sm.full[s], 1);
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.done, 1);
         fence_mbar_init();
     }
+    __syncthreads();  // barriers are initialised: the producer starts while the rest is set up
     if (warp == 5) {
         tmem_alloc(&sm.tmem_base, kMaxBatch);
         tmem_relinquish();
+        tc_fence_before();
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sm.tmem_base;
+    if (threadIdx.x < kMaxBatch) {
+        // where sequence b's values go: its row of q_out, or its new row of the cache
+        const int b = threadIdx.x;
+        long long row = -1;
+        if (b < p.B) {
+            if (which == 0) {
+                row = static_cast<long long>(b) * p.E;
+            } else {
+                const int pos = p.seq_pos ? p.seq_pos[b] : p.pos;
+                if (pos < 0 || pos >= p.T_max)
+                    report_status(p.dev_status, B2KV_DEV_BAD_POSITION);
+                else
+                    row = static_cast<long long>(b) * p.stride_b + static_cast<long long>(pos) * p.stride_t;
+            }
+        }
+        sm.row[b] = row;
+    }
 
     if (warp == 4) {
         if (lane == 0) {
             const CUtensorMap* tw = which == 0 ? &tm_wq : (which == 1 ? &tm_wk : &tm_wv);
             for (int i = 0; i < n_k; ++i) {
-                const int st = i % kStagesP;
-                if (!mbar_wait(&sm.empty[st], ((i / kStagesP) & 1) ^ 1)) break;
+                const int st = i % n_st;
+                if (!mbar_wait(&sm.empty[st], ((i / n_st) & 1) ^ 1)) break;
                 mbar_arrive_expect_tx(&sm.full[st], stage_bytes);
-                // W tile: input features i*64 .. +63 (rows), output features c0 .. c0+127 (two 64-wide boxes)
-                tma_load_2d(sm.w[st], tw, &sm.full[st], c0, i * kKTile);
-                tma_load_2d(sm.w[st] + kWHalf, tw, &sm.full[st], c0 + 64, i * kKTile);
-                // x tile: every sequence (rows past B read as zero), input features i*64 .. +63
-                tma_load_2d(sm.x[st], &tm_x, &sm.full[st], i * kKTile, 0);
+                const int k0 = i * kKTile;
+                // W tile: input features k0 .. +127 (rows), output features c0 .. c0+127 as two 64-wide boxes
+                tma_load_2d(w_ring + st * kWBytes, tw, &sm.full[st], c0, k0);
+                tma_load_2d(w_ring + st * kWBytes + kWHalf, tw, &sm.full[st], c0 + 64, k0);
+                // x tile: every sequence (rows past B read as zero), two 64-feature spans
+                tma_load_2d(x_ring + st * 2 * x_span, &tm_x, &sm.full[st], k0, 0);
+                tma_load_2d(x_ring + st * 2 * x_span + x_span, &tm_x, &sm.full[st], k0 + 64, 0);
             }
         }
         __syncwarp();
     } else if (warp == 5) {
         if (lane == 0) {
+            tc_fence_after();
+            const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sm.tmem_base);  // allocated by this warp above
             const uint32_t idesc = proj_idesc(p.Bn);
             bool ok = true;
             for (int i = 0; i < n_k && ok; ++i) {
-                const int st = i % kStagesP;
-                ok = mbar_wait(&sm.full[st], (i / kStagesP) & 1);
+                const int st = i % n_st;
+                ok = mbar_wait(&sm.full[st], (i / n_st) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                // A: [half][64 k][64 features] MN-major (halves 8 KB apart, 8 k-rows = 1024 B, 16 k = 2048 B)
-                const uint64_t da = smem_desc(smem_u32(sm.w[st]), kWHalf, 1024);
-                // B: [sequence][64 k] K-major (16 k = 32 B inside the swizzle span)
-                const uint64_t db = smem_desc(smem_u32(sm.x[st]), 16, 1024);
+                // A: [feature half][128 k][64 features] MN-major (halves 16 KB apart, 8 k-rows = 1024 B, 16 k =
+                // 2048 B).  B: [k span][sequence][64 k] K-major (16 k = 32 B inside the swizzle span).
+                const uint64_t da = smem_desc(smem_u32(w_ring + st * kWBytes), kWHalf, 1024);
+                const uint64_t db = smem_desc(smem_u32(x_ring + st * 2 * x_span), 16, 1024);
 #pragma unroll
-                for (int kk = 0; kk < kKTile / 16; ++kk)
-                    mma_ss(tmem, da + static_cast<uint64_t>((kk * 2048) >> 4), db + static_cast<uint64_t>((kk * 32) >> 4), idesc,
+                for (int kk = 0; kk < kKTile / 16; ++kk) {
+                    const uint32_t b_off = (kk >> 2) * x_span + (kk & 3) * 32;
+                    mma_ss(tmem, da + static_cast<uint64_t>((kk * 2048) >> 4), db + static_cast<uint64_t>(b_off >> 4), idesc,
                            (i | kk) ? 1u : 0u);
+                }
                 mma_commit(&sm.empty[st]);
             }
             if (ok) mma_commit(&sm.done);
@@ -136,33 +170,23 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     } else {
         // ------------------------------ epilogue: thread = output feature ------------------------------
         const int m = threadIdx.x;  // 0..127, also the TMEM lane
-        const uint32_t t_lane = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        named_barrier_sync<128>(1);  // sm.row is complete
         if (mbar_wait(&sm.done, 0)) {
             tc_fence_after();
+            // (the accumulator's address was stored by the issuing warp before its first MMA)
+            const uint32_t t_lane = sm.tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
             const int col = c0 + m;  // column inside the weight matrix = element of the output row
-            const int h = col / p.D, d = col % p.D;
-            __nv_bfloat16* q = static_cast<__nv_bfloat16*>(p.q_out);
-            __nv_bfloat16* cache = static_cast<__nv_bfloat16*>(which == 1 ? p.k_cache : p.v_cache);
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which == 0 ? p.q_out : (which == 1 ? p.k_cache : p.v_cache));
+            // inside the row: the element itself for Q, (head, head_dim element) for the cache
+            out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
             for (int nb = 0; nb < p.Bn; nb += 16) {
                 uint32_t v[16];
                 tmem_ld16(t_lane + nb, v);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int b = nb + j;
-                    if (b >= p.B) break;
-                    const __nv_bfloat16 val = __float2bfloat16_rn(__uint_as_float(v[j]));
-                    if (which == 0) {
-                        q[static_cast<size_t>(b) * p.E + col] = val;
-                    } else {
-                        const int pos = p.seq_pos ? p.seq_pos[b] : p.pos;
-                        if (pos < 0 || pos >= p.T_max) {
-                            report_status(p.dev_status, B2KV_DEV_BAD_POSITION);
-                        } else {
-                            cache[static_cast<size_t>(b) * p.stride_b + static_cast<size_t>(pos) * p.stride_t +
-                                  static_cast<size_t>(h) * p.stride_h + d] = val;
-                        }
-                    }
+                    const long long row = sm.row[nb + j];  // -1 past the batch and for positions outside the cache
+                    if (row >= 0) out[row] = __float2bfloat16_rn(__uint_as_float(v[j]));
                 }
             }
         } else {
@@ -174,7 +198,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
-        tmem_dealloc(tmem, kMaxBatch);
+        tmem_dealloc(sm.tmem_base, kMaxBatch);
     }
 }
 
@@ -212,19 +236,23 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     if (stride_b < 0 || stride_t < 0 || stride_h < 0) return B2KV_ERR_BAD_ARG;
     const int Bn = ((B + 15) / 16) * 16;  // MMA N: a multiple of 16
     CUtensorMap tq, tk, tv, tx;
-    if (!proj::make_matrix_map(&tq, wq, E, E, proj::kKTile) || !proj::make_matrix_map(&tk, wk, E, E, proj::kKTile) ||
-        !proj::make_matrix_map(&tv, wv, E, E, proj::kKTile) || !proj::make_matrix_map(&tx, x, B, E, Bn))
+    const int w_box_rows = proj::kKTile;  // 128 input features x 64 output features per box
+    if (!proj::make_matrix_map(&tq, wq, E, E, w_box_rows) || !proj::make_matrix_map(&tk, wk, E, E, w_box_rows) ||
+        !proj::make_matrix_map(&tv, wv, E, E, w_box_rows) || !proj::make_matrix_map(&tx, x, B, E, Bn))
         return B2KV_ERR_UNSUPPORTED;
-    proj::ProjParams p{q_out, k_cache, v_cache, seq_pos, dev_status, stride_b, stride_t, stride_h, pos, B, Bn, E, H, D, T_max};
-    constexpr size_t smem = sizeof(proj::ProjShared) + 1024;
-    static bool configured[64] = {false};
+    const int stage_bytes = proj::kWBytes + 2 * Bn * 128;
+    const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
+    proj::ProjParams p{q_out, k_cache, v_cache, seq_pos, dev_status, stride_b, stride_t, stride_h, pos, B, Bn, E, H, D, T_max,
+                       stages};
+    static int configured[64] = {0};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
-    if (!configured[dev]) {
+    if (configured[dev] < static_cast<int>(smem)) {
         B2KV_CUDA_TRY(cudaFuncSetAttribute(proj::qkv_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem)));
-        configured[dev] = true;
+        configured[dev] = static_cast<int>(smem);
     }
     proj::qkv_append_kernel<<<3 * E / proj::kFeat, proj::kProjThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv,
                                                                                                                    tx, p);
