@@ -222,14 +222,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     issue_qk(0, j + 1);
                 }
                 if (j < n_b) {
-                    ok = mbar_wait(&sm.p_ready[1], j & 1) && mbar_wait(&sm.v_full[st], par);
+                    // (a wait costs the issuing thread about 100 clocks even when the barrier is long complete,
+                    // and the tensor pipe idles meanwhile: V and K are only waited for once per step)
+                    ok = mbar_wait(&sm.p_ready[1], j & 1) && (j < n_a || mbar_wait(&sm.v_full[st], par));
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(1, j);
                 }
                 mma_commit(&sm.v_empty[st]);
                 if (j + 1 < n_b) {
-                    ok = mbar_wait(&sm.k_full[st1], par1);
+                    ok = j + 1 < n_a || mbar_wait(&sm.k_full[st1], par1);
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(1, j + 1);
