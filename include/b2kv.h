@@ -247,6 +247,17 @@ int b2kv_qkv_append(const void* x, const void* wq, const void* wk, const void* w
                     int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
 
 /*
+ * out[b, :] = x[b, :] @ w (+ residual[b, :]) for the few rows of a decode step: x [B, K], w [K, N] row-major,
+ * residual (nullable) and out [B, N], bf16 with fp32 accumulation, B <= 128, K and N multiples of 128.
+ * Replaces the reference's matmul dispatch (simple-llm/src/gpu/gpu_pass_forward.py:35-82, C = A @ B) for the
+ * attention output projection and the MLP of a cached decode step (src/wgpu_backend.py:857-905), and with
+ * `residual` also the residual_add that follows (gpu_pass_forward.py:250-283).  Same kernel as
+ * b2kv_qkv_append (the weights are streamed once through the tensor cores).
+ */
+int b2kv_matmul_rows(const void* x, const void* w, const void* residual, void* out, int B, int K, int N, int dtype,
+                     void* stream);
+
+/*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,

@@ -20,6 +20,10 @@
 //     sequence (consecutive lanes write consecutive head_dim elements), so the new K / V never
 //     make a round trip through HBM;
 //   * every wait is bounded; a position outside the cache is skipped and recorded in the status word.
+//
+// The same kernel with one weight matrix [K, N] is the plain product of a decode step's rows with a
+// weight matrix (b2kv_matmul_rows: the attention output projection and the MLP), optionally with a
+// residual added before rounding.
 #include "b2kv_common.cuh"
 #include "tc_ptx.cuh"
 #include "tma_map.cuh"
@@ -59,7 +63,9 @@ struct ProjParams {
     const int32_t* seq_pos;
     int32_t* dev_status;
     int64_t stride_b, stride_t, stride_h;
-    int pos, B, Bn, E, H, D, T_max;
+    int pos, B, Bn, E, H, D, T_max;  // E = columns of a weight matrix (output features of one matrix)
+    int k_in;                         // rows of a weight matrix (input features)
+    const void* residual;             // [B, E] added to the product of the single-matrix form, or null
     int stages;
 };
 
@@ -86,7 +92,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     const int f0 = blockIdx.x * kFeat;  // first output feature, in the concatenation Wq | Wk | Wv
     const int which = f0 / p.E;         // 0 = Q, 1 = K, 2 = V
     const int c0 = f0 % p.E;            // first column inside that weight matrix
-    const int n_k = p.E / kKTile;
+    const int n_k = p.k_in / kKTile;
     const uint32_t x_span = static_cast<uint32_t>(p.Bn) * 128u;  // Bn rows of one 64-feature span
     uint8_t* const x_ring = w_ring + p.stages * kWBytes;
     const int n_st = p.stages;
@@ -179,6 +185,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which == 0 ? p.q_out : (which == 1 ? p.k_cache : p.v_cache));
             // inside the row: the element itself for Q, (head, head_dim element) for the cache
             out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
+            const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
             for (int nb = 0; nb < p.Bn; nb += 16) {
                 uint32_t v[16];
                 tmem_ld16(t_lane + nb, v);
@@ -186,7 +193,11 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const long long row = sm.row[nb + j];  // -1 past the batch and for positions outside the cache
-                    if (row >= 0) out[row] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                    if (row >= 0) {
+                        float acc = __uint_as_float(v[j]);
+                        if (res != nullptr) acc += __bfloat162float(res[row]);
+                        out[row] = __float2bfloat16_rn(acc);
+                    }
                 }
             }
         } else {
@@ -213,6 +224,17 @@ static bool make_matrix_map(CUtensorMap* map, const void* base, int rows, int co
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Raises the kernel's dynamic shared memory limit on this device when a larger ring is asked for.
+static cudaError_t configure_smem(int dev, size_t smem) {
+    static int configured[64] = {0};
+    if (configured[dev] < static_cast<int>(smem)) {
+        cudaError_t e = cudaFuncSetAttribute(qkv_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        configured[dev] = static_cast<int>(smem);
+    }
+    return cudaSuccess;
 }
 
 }  // namespace proj
@@ -244,18 +266,38 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     proj::ProjParams p{q_out, k_cache, v_cache, seq_pos, dev_status, stride_b, stride_t, stride_h, pos, B, Bn, E, H, D, T_max,
-                       stages};
-    static int configured[64] = {0};
+                       E, nullptr, stages};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
-    if (configured[dev] < static_cast<int>(smem)) {
-        B2KV_CUDA_TRY(cudaFuncSetAttribute(proj::qkv_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem)));
-        configured[dev] = static_cast<int>(smem);
-    }
+    B2KV_CUDA_TRY(proj::configure_smem(dev, smem));
     proj::qkv_append_kernel<<<3 * E / proj::kFeat, proj::kProjThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv,
                                                                                                                    tx, p);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
+extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* residual, void* out, int B, int K, int N, int dtype,
+                                void* stream) {
+    if (dtype != B2KV_DTYPE_BF16) return B2KV_ERR_UNSUPPORTED;
+    if (!x || !w || !out) return B2KV_ERR_BAD_ARG;
+    if (B <= 0 || K <= 0 || N <= 0) return B2KV_ERR_BAD_ARG;
+    if (B > proj::kMaxBatch || K % proj::kKTile != 0 || N % proj::kFeat != 0) return B2KV_ERR_UNSUPPORTED;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(out) || !aligned16(residual)) return B2KV_ERR_ALIGN;
+    const int Bn = ((B + 15) / 16) * 16;
+    CUtensorMap tw, tx;
+    if (!proj::make_matrix_map(&tw, w, K, N, proj::kKTile) || !proj::make_matrix_map(&tx, x, B, K, Bn))
+        return B2KV_ERR_UNSUPPORTED;
+    const int stage_bytes = proj::kWBytes + 2 * Bn * 128;
+    const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
+    // one weight matrix: every tile is of kind 0 (plain rows of `out`); the cache fields are unused
+    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, stages};
+    int dev = 0;
+    B2KV_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
+    B2KV_CUDA_TRY(proj::configure_smem(dev, smem));
+    proj::qkv_append_kernel<<<N / proj::kFeat, proj::kProjThreads, smem, static_cast<cudaStream_t>(stream)>>>(tw, tw, tw, tx, p);
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
 }

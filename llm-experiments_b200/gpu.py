@@ -21,7 +21,7 @@ from .kv_cache import (
     kv_cache_set_lengths,
     kv_cache_update,
 )
-from .projection import qkv_project_append
+from .projection import matmul, qkv_project_append
 from .step_tail import argmax, extract_last_tokens, layernorm, softmax
 from .types import GPUBuffer1D, GPUBuffer2D, GPUConfig, GPUContext, KVCache, KVCacheConfig, KVCacheLayer
 
@@ -35,5 +35,5 @@ __all__ = [
     "kv_cache_create", "kv_cache_reset", "kv_cache_update", "attention_with_kv_cache",
     "kv_cache_gather", "kv_cache_set_lengths",
     "layernorm", "extract_last_tokens", "softmax", "argmax",
-    "qkv_project_append",
+    "qkv_project_append", "matmul",
 ]

@@ -18,6 +18,35 @@ from .kv_cache import _ptr, cache_strides, dtype_code
 from .types import GPUBuffer2D, GPUContext, KVCache
 
 
+def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, residual: GPUBuffer2D = None) -> None:
+    """``C = A @ B`` with the reference's argument order and shape check
+    (simple-llm/src/gpu/gpu_pass_forward.py:35-82), for the shapes of a cached decode step: bfloat16,
+    at most 128 rows in ``A``, inner and outer dimensions multiples of 128.  ``residual`` (extension)
+    is added to the product before rounding, which also replaces the ``residual_add`` that follows
+    the output projection and the MLP in the reference's block (src/wgpu_backend.py:857-905)."""
+    M, K = A.shape
+    K2, N = B.shape
+    # same checks and texts as validate_matmul_shapes (simple-llm/src/gpu/gpu_ops.py:84-99)
+    if M <= 0 or K <= 0 or N <= 0 or K2 <= 0:
+        raise ValueError(f"matmul: Invalid dimensions A=({M}, {K}), B=({K2}, {N})")
+    if K != K2:
+        raise ValueError(f"matmul: Dimension mismatch A.shape[1]={K} != B.shape[0]={K2}")
+    if tuple(C.shape) != (M, N):
+        raise ValueError(f"matmul: Output shape {C.shape} doesn't match expected ({M}, {N})")
+    if residual is not None:
+        validate_buffer_shape_2d(residual, (M, N), "residual")
+    bufs = [A, B, C] + ([residual] if residual is not None else [])
+    if any(t.buffer.dtype != torch.bfloat16 for t in bufs):
+        raise ValueError("matmul takes bfloat16 buffers")
+    if M > 128 or K % 128 != 0 or N % 128 != 0:
+        raise ValueError("matmul covers decode-step shapes: at most 128 rows, K and N multiples of 128")
+    stream = batch_op_begin(ctx)
+    rc = _native.lib.b2kv_matmul_rows(A.buffer.data_ptr(), B.buffer.data_ptr(),
+                                      None if residual is None else residual.buffer.data_ptr(), C.buffer.data_ptr(),
+                                      M, K, N, dtype_code(torch.bfloat16), stream)
+    _native.check(rc)
+
+
 def qkv_project_append(ctx: GPUContext, cache: KVCache, layer_idx: int, x: GPUBuffer2D, wq: GPUBuffer2D,
                        wk: GPUBuffer2D, wv: GPUBuffer2D, q_out: GPUBuffer2D, advance: bool = True) -> None:
     """``q_out = x @ wq``; row ``current_len`` (or ``seq_lens[b]``) of the layer's K / V cache

@@ -89,3 +89,36 @@ def test_qkv_project_append_checks(pkg, ctx):
     with pytest.raises(ValueError, match="Cache is full"):
         gpu.qkv_project_append(ctx, cache, 0, x, w, w, w, q)
     gpu.batch_commit(ctx)
+
+
+@pytest.mark.parametrize("M,K,N,with_residual", [(64, 1024, 512, False), (5, 128, 256, True), (128, 512, 128, True),
+                                                 (1, 4096, 1024, False), (33, 256, 1280, True)])
+def test_matmul_rows_vs_oracle(pkg, ctx, M, K, N, with_residual):
+    gpu = pkg.gpu
+    A = _bf16(ctx, (M, K), 11)
+    W = _bf16(ctx, (K, N), 12, scale=K ** -0.5)
+    R = _bf16(ctx, (M, N), 13) if with_residual else None
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device=ctx.device)
+    gpu.batch_begin(ctx)
+    gpu.matmul(ctx, U.buf2d(pkg, ctx, A), U.buf2d(pkg, ctx, W), U.buf2d(pkg, ctx, C),
+               residual=None if R is None else U.buf2d(pkg, ctx, R))
+    gpu.batch_commit(ctx)
+    want = U.to_f32(A).astype(np.float64) @ U.to_f32(W).astype(np.float64)
+    if R is not None:
+        want = want + U.to_f32(R)
+    np.testing.assert_allclose(U.to_f32(C), want.astype(np.float32), rtol=RTOL, atol=ATOL)
+
+
+def test_matmul_checks(pkg, ctx):
+    gpu = pkg.gpu
+    mk = lambda r, c, dt=torch.bfloat16: U.buf2d(pkg, ctx, torch.zeros((r, c), dtype=dt, device=ctx.device))  # noqa: E731
+    gpu.batch_begin(ctx)
+    with pytest.raises(ValueError, match=r"matmul: Dimension mismatch A.shape\[1\]=128 != B.shape\[0\]=256"):
+        gpu.matmul(ctx, mk(4, 128), mk(256, 128), mk(4, 128))
+    with pytest.raises(ValueError, match="matmul: Output shape"):
+        gpu.matmul(ctx, mk(4, 128), mk(128, 128), mk(4, 256))
+    with pytest.raises(ValueError, match="bfloat16"):
+        gpu.matmul(ctx, mk(4, 128, torch.float32), mk(128, 128), mk(4, 128))
+    with pytest.raises(ValueError, match="decode-step shapes"):
+        gpu.matmul(ctx, mk(4, 64), mk(64, 128), mk(4, 128))
+    gpu.batch_commit(ctx)
