@@ -227,6 +227,9 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
  */
 int b2kv_layernorm(const float* x, const float* gamma, const float* beta, float* out, int64_t n_rows, int size,
                    float epsilon, void* stream);
+/* b2kv_layernorm on bf16 rows and bf16 gamma / beta (fp32 arithmetic): extension for bf16 decoder layers. */
+int b2kv_layernorm_bf16(const void* x, const void* gamma, const void* beta, void* out, int64_t n_rows, int size,
+                        float epsilon, void* stream);
 int b2kv_extract_last_tokens(const float* in, float* out, int batch_size, int seq_len, int embedding_dim, void* stream);
 int b2kv_softmax(const float* logits, float* probs, int64_t n_rows, int size, void* stream);
 int b2kv_argmax(const float* x, int32_t* out, int n_rows, int size, void* stream);
@@ -247,15 +250,16 @@ int b2kv_qkv_append(const void* x, const void* wq, const void* wk, const void* w
                     int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
 
 /*
- * out[b, :] = x[b, :] @ w (+ residual[b, :]) for the few rows of a decode step: x [B, K], w [K, N] row-major,
- * residual (nullable) and out [B, N], bf16 with fp32 accumulation, B <= 128, K and N multiples of 128.
- * Replaces the reference's matmul dispatch (simple-llm/src/gpu/gpu_pass_forward.py:35-82, C = A @ B) for the
- * attention output projection and the MLP of a cached decode step (src/wgpu_backend.py:857-905), and with
- * `residual` also the residual_add that follows (gpu_pass_forward.py:250-283).  Same kernel as
- * b2kv_qkv_append (the weights are streamed once through the tensor cores).
+ * out[b, :] = act(x[b, :] @ w + bias) + residual[b, :] for the few rows of a decode step: x [B, K], w [K, N]
+ * row-major, bias [N] (nullable), residual (nullable) and out [B, N]; activation 0 = none, 1 = the reference's GELU
+ * x * sigmoid(1.702 x) (src/gpu/gpu_kernels.py:285-293); bf16 with fp32 accumulation, B <= 128, K and N multiples
+ * of 128.  Replaces the reference's matmul dispatch (simple-llm/src/gpu/gpu_pass_forward.py:35-82, C = A @ B)
+ * for the attention output projection and the MLP of a cached decode step (src/wgpu_backend.py:857-930), together
+ * with the bias_add (:211-248), gelu (:179-209) and residual_add (:250-283) dispatches that follow it there.
+ * Same kernel as b2kv_qkv_append (the weights are streamed once through the tensor cores).
  */
-int b2kv_matmul_rows(const void* x, const void* w, const void* residual, void* out, int B, int K, int N, int dtype,
-                     void* stream);
+int b2kv_matmul_rows(const void* x, const void* w, const void* bias, const void* residual, void* out, int B, int K, int N,
+                     int activation, int dtype, void* stream);
 
 /*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",

@@ -55,11 +55,12 @@ SIGNATURES = {
     "b2kv_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp]),
     "b2kv_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),
+    "b2kv_layernorm_bf16": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),
     "b2kv_extract_last_tokens": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "b2kv_softmax": (_i, [_vp, _vp, _i64, _i, _vp]),
     "b2kv_argmax": (_i, [_vp, _vp, _i, _i, _vp]),
     "b2kv_qkv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
-    "b2kv_matmul_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "b2kv_matmul_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "b2kv_tune": (_i, [ctypes.c_char_p, _i]),
 }
 

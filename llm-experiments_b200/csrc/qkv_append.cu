@@ -66,6 +66,8 @@ struct ProjParams {
     int pos, B, Bn, E, H, D, T_max;  // E = columns of a weight matrix (output features of one matrix)
     int k_in;                         // rows of a weight matrix (input features)
     const void* residual;             // [B, E] added to the product of the single-matrix form, or null
+    const void* bias;                 // [E] added before the activation, or null
+    int gelu;                         // x * sigmoid(1.702 x) after the bias (simple-llm/src/gpu/gpu_kernels.py:285-293)
     int stages;
 };
 
@@ -186,6 +188,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             // inside the row: the element itself for Q, (head, head_dim element) for the cache
             out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
             const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
+            const float bias = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : 0.f;
             for (int nb = 0; nb < p.Bn; nb += 16) {
                 uint32_t v[16];
                 tmem_ld16(t_lane + nb, v);
@@ -194,7 +197,8 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
                 for (int j = 0; j < 16; ++j) {
                     const long long row = sm.row[nb + j];  // -1 past the batch and for positions outside the cache
                     if (row >= 0) {
-                        float acc = __uint_as_float(v[j]);
+                        float acc = __uint_as_float(v[j]) + bias;
+                        if (p.gelu) acc = acc / (1.0f + __expf(-1.702f * acc));
                         if (res != nullptr) acc += __bfloat162float(res[row]);
                         out[row] = __float2bfloat16_rn(acc);
                     }
@@ -266,7 +270,7 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     proj::ProjParams p{q_out, k_cache, v_cache, seq_pos, dev_status, stride_b, stride_t, stride_h, pos, B, Bn, E, H, D, T_max,
-                       E, nullptr, stages};
+                       E, nullptr, nullptr, 0, stages};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
@@ -277,13 +281,13 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     return B2KV_OK;
 }
 
-extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* residual, void* out, int B, int K, int N, int dtype,
-                                void* stream) {
+extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* bias, const void* residual, void* out, int B, int K,
+                                int N, int activation, int dtype, void* stream) {
     if (dtype != B2KV_DTYPE_BF16) return B2KV_ERR_UNSUPPORTED;
     if (!x || !w || !out) return B2KV_ERR_BAD_ARG;
-    if (B <= 0 || K <= 0 || N <= 0) return B2KV_ERR_BAD_ARG;
+    if (B <= 0 || K <= 0 || N <= 0 || activation < 0 || activation > 1) return B2KV_ERR_BAD_ARG;
     if (B > proj::kMaxBatch || K % proj::kKTile != 0 || N % proj::kFeat != 0) return B2KV_ERR_UNSUPPORTED;
-    if (!aligned16(x) || !aligned16(w) || !aligned16(out) || !aligned16(residual)) return B2KV_ERR_ALIGN;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(out) || !aligned16(residual) || !aligned16(bias)) return B2KV_ERR_ALIGN;
     const int Bn = ((B + 15) / 16) * 16;
     CUtensorMap tw, tx;
     if (!proj::make_matrix_map(&tw, w, K, N, proj::kKTile) || !proj::make_matrix_map(&tx, x, B, K, Bn))
@@ -292,7 +296,7 @@ extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* residu
     const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     // one weight matrix: every tile is of kind 0 (plain rows of `out`); the cache fields are unused
-    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, stages};
+    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, bias, activation, stages};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;

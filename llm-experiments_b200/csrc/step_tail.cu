@@ -1,5 +1,6 @@
 // The tail of a cached generation step: layer normalisation, last-token extraction, softmax over
-// the vocabulary and argmax.  fp32 like the reference's buffers (simple-llm/src/gpu/gpu_buffer.py:31-39).
+// the vocabulary and argmax.  fp32 like the reference's buffers (simple-llm/src/gpu/gpu_buffer.py:31-39);
+// layer normalisation also takes bf16 rows and parameters (fp32 arithmetic) for a bf16 decoder layer.
 //
 // Reference kernels (simple-llm/src/gpu/gpu_kernels.py): layernorm :137-249 (one workgroup per row,
 // mean by tree reduction, then the variance of (x - mean), then (x - mean) / sqrt(var + eps) * gamma
@@ -47,18 +48,38 @@ __device__ __forceinline__ float row_reduce(float v, float* scratch) {
     return r;
 }
 
+// Four consecutive elements as floats (16 bytes of fp32 or 8 bytes of bf16), and back.
+__device__ __forceinline__ float4 load4(const float* p, int i) { return reinterpret_cast<const float4*>(p)[i]; }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p, int i) {
+    const uint2 u = reinterpret_cast<const uint2*>(p)[i];
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, int i, float4 v) { reinterpret_cast<float4*>(p)[i] = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, int i, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(p)[i] = u;
+}
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void from_f(float* p, float v) { *p = v; }
+__device__ __forceinline__ void from_f(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
 // mode 0: layernorm (a = gamma, b = beta); mode 1: softmax
-template <int kMode, int kTpr>
-__global__ void __launch_bounds__(kCtaThreads) row_kernel(const float* __restrict__ x, const float* __restrict__ ga,
-                                                         const float* __restrict__ be, float* __restrict__ y,
+template <int kMode, int kTpr, typename T>
+__global__ void __launch_bounds__(kCtaThreads) row_kernel(const T* __restrict__ x, const T* __restrict__ ga,
+                                                         const T* __restrict__ be, T* __restrict__ y,
                                                          int64_t rows, int size, float eps) {
     __shared__ float scratch[kCtaThreads / 32];
     constexpr int kRowsPerCta = kCtaThreads / kTpr;
     const int t = threadIdx.x % kTpr;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + threadIdx.x / kTpr;
     const bool live = row < rows;  // dead threads still take part in the barriers
-    const float* xr = x + (live ? row : 0) * size;
-    float* yr = y + (live ? row : 0) * size;
+    const T* xr = x + (live ? row : 0) * size;
+    T* yr = y + (live ? row : 0) * size;
     const bool vec = (size % 4 == 0);  // rows of a 16-byte aligned matrix then start on 16 bytes
     const int chunks = vec ? size / 4 : 0;
     const bool in_regs = vec && chunks <= kMaxRegChunks * kTpr;
@@ -71,13 +92,13 @@ __global__ void __launch_bounds__(kCtaThreads) row_kernel(const float* __restric
         for (int c = 0; c < kMaxRegChunks; ++c) {
             const int i = t + c * kTpr;
             if (live && i < chunks) {
-                const float4 v = reinterpret_cast<const float4*>(xr)[i];
+                const float4 v = load4(xr, i);
                 keep[c] = v;
                 acc = kMode == 0 ? acc + ((v.x + v.y) + (v.z + v.w)) : fmaxf(acc, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
             }
         }
     } else if (live) {
-        for (int i = t; i < size; i += kTpr) acc = kMode == 0 ? acc + xr[i] : fmaxf(acc, xr[i]);
+        for (int i = t; i < size; i += kTpr) acc = kMode == 0 ? acc + to_f(xr[i]) : fmaxf(acc, to_f(xr[i]));
     }
     const float first = kMode == 0 ? row_reduce<SumOp, kTpr>(acc, scratch) / static_cast<float>(size)
                                    : row_reduce<MaxOp, kTpr>(acc, scratch);  // mean or maximum
@@ -100,7 +121,7 @@ __global__ void __launch_bounds__(kCtaThreads) row_kernel(const float* __restric
         }
     } else if (live) {
         for (int i = t; i < size; i += kTpr) {
-            const float d = xr[i] - first;
+            const float d = to_f(xr[i]) - first;
             acc += kMode == 0 ? d * d : expf(d);
         }
     }
@@ -114,26 +135,25 @@ __global__ void __launch_bounds__(kCtaThreads) row_kernel(const float* __restric
             if (live && i < chunks) {
                 float4 v = keep[c];
                 if (kMode == 0) {
-                    const float4 g = reinterpret_cast<const float4*>(ga)[i], b = reinterpret_cast<const float4*>(be)[i];
+                    const float4 g = load4(ga, i), b = load4(be, i);
                     v.x = v.x * scale * g.x + b.x, v.y = v.y * scale * g.y + b.y;
                     v.z = v.z * scale * g.z + b.z, v.w = v.w * scale * g.w + b.w;
                 } else {
                     v.x /= scale, v.y /= scale, v.z /= scale, v.w /= scale;
                 }
-                reinterpret_cast<float4*>(yr)[i] = v;
+                store4(yr, i, v);
             }
         }
     } else if (live) {
         for (int i = t; i < size; i += kTpr) {
-            const float d = xr[i] - first;
-            yr[i] = kMode == 0 ? d * scale * ga[i] + be[i] : expf(d) / scale;
+            const float d = to_f(xr[i]) - first;
+            from_f(&yr[i], kMode == 0 ? d * scale * to_f(ga[i]) + to_f(be[i]) : expf(d) / scale);
         }
     }
 }
 
-template <int kMode>
-int launch_rows(const float* x, const float* ga, const float* be, float* y, int64_t rows, int size, float eps,
-                cudaStream_t stream) {
+template <int kMode, typename T>
+int launch_rows(const T* x, const T* ga, const T* be, T* y, int64_t rows, int size, float eps, cudaStream_t stream) {
     // threads per row by row length (in 16-byte chunks when the row can be vectorised)
     const int work = size % 4 == 0 ? size / 4 : size;
     const int tpr = work <= 64 ? 32 : (work <= 256 ? 64 : (work <= 1024 ? 128 : 256));
@@ -141,10 +161,10 @@ int launch_rows(const float* x, const float* ga, const float* be, float* y, int6
     if (ctas > 0x7fffffffLL) return B2KV_ERR_UNSUPPORTED;
     const unsigned grid = static_cast<unsigned>(ctas);
     switch (tpr) {
-        case 32: row_kernel<kMode, 32><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
-        case 64: row_kernel<kMode, 64><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
-        case 128: row_kernel<kMode, 128><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
-        default: row_kernel<kMode, 256><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
+        case 32: row_kernel<kMode, 32, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
+        case 64: row_kernel<kMode, 64, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
+        case 128: row_kernel<kMode, 128, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
+        default: row_kernel<kMode, 256, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
     }
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
@@ -199,14 +219,24 @@ extern "C" int b2kv_layernorm(const float* x, const float* gamma, const float* b
     if (!x || !gamma || !beta || !out) return B2KV_ERR_BAD_ARG;
     if (n_rows <= 0 || size <= 0) return B2KV_ERR_BAD_ARG;
     if (!aligned16(x) || !aligned16(gamma) || !aligned16(beta) || !aligned16(out)) return B2KV_ERR_ALIGN;
-    return launch_rows<0>(x, gamma, beta, out, n_rows, size, epsilon, static_cast<cudaStream_t>(stream));
+    return launch_rows<0, float>(x, gamma, beta, out, n_rows, size, epsilon, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b2kv_layernorm_bf16(const void* x, const void* gamma, const void* beta, void* out, int64_t n_rows, int size,
+                                   float epsilon, void* stream) {
+    if (!x || !gamma || !beta || !out) return B2KV_ERR_BAD_ARG;
+    if (n_rows <= 0 || size <= 0) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(x) || !aligned16(gamma) || !aligned16(beta) || !aligned16(out)) return B2KV_ERR_ALIGN;
+    using T = __nv_bfloat16;
+    return launch_rows<0, T>(static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta),
+                             static_cast<T*>(out), n_rows, size, epsilon, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b2kv_softmax(const float* logits, float* probs, int64_t n_rows, int size, void* stream) {
     if (!logits || !probs) return B2KV_ERR_BAD_ARG;
     if (n_rows <= 0 || size <= 0) return B2KV_ERR_BAD_ARG;
     if (!aligned16(logits) || !aligned16(probs)) return B2KV_ERR_ALIGN;
-    return launch_rows<1>(logits, nullptr, nullptr, probs, n_rows, size, 0.f, static_cast<cudaStream_t>(stream));
+    return launch_rows<1, float>(logits, static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), probs, n_rows, size, 0.f, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b2kv_extract_last_tokens(const float* in, float* out, int batch_size, int seq_len, int embedding_dim,

@@ -18,12 +18,15 @@ from .kv_cache import _ptr, cache_strides, dtype_code
 from .types import GPUBuffer2D, GPUContext, KVCache
 
 
-def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, residual: GPUBuffer2D = None) -> None:
+def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, residual: GPUBuffer2D = None,
+           bias=None, activation: str = None) -> None:
     """``C = A @ B`` with the reference's argument order and shape check
     (simple-llm/src/gpu/gpu_pass_forward.py:35-82), for the shapes of a cached decode step: bfloat16,
-    at most 128 rows in ``A``, inner and outer dimensions multiples of 128.  ``residual`` (extension)
-    is added to the product before rounding, which also replaces the ``residual_add`` that follows
-    the output projection and the MLP in the reference's block (src/wgpu_backend.py:857-905)."""
+    at most 128 rows in ``A``, inner and outer dimensions multiples of 128.  Extensions that fold the
+    dispatches which follow a matmul in the reference's block (src/wgpu_backend.py:857-930) into
+    it: ``bias`` (a ``GPUBuffer1D`` of N values, ``bias_add``), ``activation="gelu"``
+    (``x * sigmoid(1.702 x)``, ``gelu``) and ``residual`` (``residual_add``), applied in that order:
+    ``C = act(A @ B + bias) + residual``."""
     M, K = A.shape
     K2, N = B.shape
     # same checks and texts as validate_matmul_shapes (simple-llm/src/gpu/gpu_ops.py:84-99)
@@ -35,15 +38,20 @@ def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, resi
         raise ValueError(f"matmul: Output shape {C.shape} doesn't match expected ({M}, {N})")
     if residual is not None:
         validate_buffer_shape_2d(residual, (M, N), "residual")
-    bufs = [A, B, C] + ([residual] if residual is not None else [])
+    if bias is not None and tuple(bias.shape) != (N,):
+        raise ValueError(f"bias shape mismatch: expected ({N},), got {tuple(bias.shape)}")
+    if activation not in (None, "gelu"):
+        raise ValueError(f"unknown activation {activation!r}")
+    bufs = [A, B, C] + [t for t in (residual, bias) if t is not None]
     if any(t.buffer.dtype != torch.bfloat16 for t in bufs):
         raise ValueError("matmul takes bfloat16 buffers")
     if M > 128 or K % 128 != 0 or N % 128 != 0:
         raise ValueError("matmul covers decode-step shapes: at most 128 rows, K and N multiples of 128")
     stream = batch_op_begin(ctx)
     rc = _native.lib.b2kv_matmul_rows(A.buffer.data_ptr(), B.buffer.data_ptr(),
+                                      None if bias is None else bias.buffer.data_ptr(),
                                       None if residual is None else residual.buffer.data_ptr(), C.buffer.data_ptr(),
-                                      M, K, N, dtype_code(torch.bfloat16), stream)
+                                      M, K, N, 1 if activation == "gelu" else 0, dtype_code(torch.bfloat16), stream)
     _native.check(rc)
 
 

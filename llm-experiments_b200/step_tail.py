@@ -32,9 +32,17 @@ def layernorm(ctx: GPUContext, input_buf: GPUBuffer2D, gamma: GPUBuffer1D, beta:
     validate_buffer_shape_1d(gamma, size, "gamma")
     validate_buffer_shape_1d(beta, size, "beta")
     validate_buffer_shape_2d(output, (n_elements, size), "output")
-    ptrs = (_f32(input_buf, "input_buf"), _f32(gamma, "gamma"), _f32(beta, "beta"), _f32(output, "output"))
+    bufs = (input_buf, gamma, beta, output)
+    if all(t.buffer.dtype == torch.bfloat16 for t in bufs):
+        # extension: bf16 rows and parameters, fp32 arithmetic
+        if not all(t.buffer.is_contiguous() for t in bufs):
+            raise ValueError("layernorm buffers must be contiguous")
+        fn, ptrs = _native.lib.b2kv_layernorm_bf16, tuple(t.buffer.data_ptr() for t in bufs)
+    else:
+        fn = _native.lib.b2kv_layernorm
+        ptrs = (_f32(input_buf, "input_buf"), _f32(gamma, "gamma"), _f32(beta, "beta"), _f32(output, "output"))
     stream = batch_op_begin(ctx)
-    _native.check(_native.lib.b2kv_layernorm(*ptrs, n_elements, size, float(ctx.config.layernorm_epsilon), stream))
+    _native.check(fn(*ptrs, n_elements, size, float(ctx.config.layernorm_epsilon), stream))
 
 
 def extract_last_tokens(ctx: GPUContext, input_buf: GPUBuffer2D, output: GPUBuffer2D, batch_size: int, seq_len: int,

@@ -1,0 +1,60 @@
+"""One decoder layer of a cached decode step (layernorm, fused Q/K/V projection + append, cached attention,
+output projection + residual, layernorm, MLP with GELU + residual) against the numpy restatement of the
+reference block that rounds to bf16 at the same places.  Tolerance: 2^-6 relative + 3e-2 absolute (seven
+bf16-rounded stages; a single bf16 rounding is 2^-9 relative)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import decode_layer_oracle
+from tests import kv_util as U
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,H,D,ragged", [(5, 2, 64, True), (16, 4, 128, False)])
+def test_decoder_layer_step_vs_oracle(pkg, B, H, D, ragged):
+    from llm_experiments_b200 import decode_layer
+
+    gpu = pkg.gpu
+    ctx = U.make_ctx(pkg)
+    E, T_max = H * D, 48
+    g = torch.Generator().manual_seed(B)
+    rnd = lambda shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(ctx.device)  # noqa: E731
+    b2 = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    b1 = lambda t: gpu.GPUBuffer1D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    raw = dict(ln1_gamma=rnd((E,), 0.2) + 1, ln1_beta=rnd((E,), 0.1), wq=rnd((E, E), E ** -0.5), wk=rnd((E, E), E ** -0.5),
+               wv=rnd((E, E), E ** -0.5), wo=rnd((E, E), E ** -0.5), ln2_gamma=rnd((E,), 0.2) + 1, ln2_beta=rnd((E,), 0.1),
+               w1=rnd((E, 4 * E), E ** -0.5), b1=rnd((4 * E,), 0.1), w2=rnd((4 * E, E), (4 * E) ** -0.5), b2=rnd((E,), 0.1))
+    w = decode_layer.DecoderLayerWeights(**{k: (b1(v) if v.dim() == 1 else b2(v)) for k, v in raw.items()})
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=torch.bfloat16, layout="bhtd", ragged=ragged))
+    layer = cache.layers[0]
+    layer.k_cache.buffer.copy_(rnd(tuple(layer.k_cache.buffer.shape)))
+    layer.v_cache.buffer.copy_(rnd(tuple(layer.v_cache.buffer.shape)))
+    rng = np.random.default_rng(B)
+    if ragged:
+        lens = rng.integers(0, T_max - 1, size=B).astype(np.int32)
+        gpu.kv_cache_set_lengths(cache, lens)
+    else:
+        lens = np.full(B, 11, dtype=np.int32)
+        cache.current_len = 11
+    k_before = U.to_f32(U.logical_view(cache, layer, "k")).reshape(B, T_max, E)
+    v_before = U.to_f32(U.logical_view(cache, layer, "v")).reshape(B, T_max, E)
+    x = rnd((B, E))
+    y = torch.empty_like(x)
+    scratch = decode_layer.decoder_layer_scratch(ctx, B, E)
+    gpu.batch_begin(ctx)
+    decode_layer.decoder_layer_step(ctx, cache, b2(x), w, scratch, b2(y))
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    wf = {k: U.to_f32(v) for k, v in raw.items()}
+    want_y, want_k, want_v = decode_layer_oracle.decoder_layer_step(U.to_f32(x), wf, list(k_before), list(v_before), lens, H)
+    np.testing.assert_allclose(U.to_f32(y), want_y, rtol=2.0 ** -6, atol=3e-2)
+    k_after = U.to_f32(U.logical_view(cache, layer, "k")).reshape(B, T_max, E)
+    rows = np.arange(B)
+    np.testing.assert_allclose(k_after[rows, lens], want_k, rtol=2.0 ** -7, atol=1e-2)
+    if ragged:
+        assert np.array_equal(cache.seq_lens.cpu().numpy(), lens + 1)
+    else:
+        assert cache.current_len == 12

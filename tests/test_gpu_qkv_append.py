@@ -109,6 +109,22 @@ def test_matmul_rows_vs_oracle(pkg, ctx, M, K, N, with_residual):
     np.testing.assert_allclose(U.to_f32(C), want.astype(np.float32), rtol=RTOL, atol=ATOL)
 
 
+def test_matmul_with_bias_gelu_and_residual_like_the_mlp(pkg, ctx):
+    """C = gelu(A @ W + b) + R, the reference's matmul -> bias_add -> gelu (-> residual_add) chain."""
+    gpu = pkg.gpu
+    M, K, N = 64, 512, 1024
+    A, W = _bf16(ctx, (M, K), 21), _bf16(ctx, (K, N), 22, scale=K ** -0.5)
+    bias, R = _bf16(ctx, (N,), 23), _bf16(ctx, (M, N), 24)
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device=ctx.device)
+    gpu.batch_begin(ctx)
+    gpu.matmul(ctx, U.buf2d(pkg, ctx, A), U.buf2d(pkg, ctx, W), U.buf2d(pkg, ctx, C), residual=U.buf2d(pkg, ctx, R),
+               bias=gpu.GPUBuffer1D(buffer=bias, shape=(N,), size=N), activation="gelu")
+    gpu.batch_commit(ctx)
+    z = U.to_f32(A).astype(np.float64) @ U.to_f32(W).astype(np.float64) + U.to_f32(bias)
+    want = z / (1.0 + np.exp(-1.702 * z)) + U.to_f32(R)
+    np.testing.assert_allclose(U.to_f32(C), want.astype(np.float32), rtol=RTOL, atol=ATOL)
+
+
 def test_matmul_checks(pkg, ctx):
     gpu = pkg.gpu
     mk = lambda r, c, dt=torch.bfloat16: U.buf2d(pkg, ctx, torch.zeros((r, c), dtype=dt, device=ctx.device))  # noqa: E731

@@ -110,3 +110,21 @@ def test_argmax_takes_the_lowest_index_among_equals(pkg, ctx):
     gpu.argmax(ctx, gpu.gpu_buffer_2d_create(ctx, 37, 50257, _dev(ctx, x)), idx)
     gpu.batch_commit(ctx)
     assert np.array_equal(idx.buffer.cpu().numpy(), T.argmax(x))
+
+
+@pytest.mark.parametrize("n,size", [(64, 4096), (5, 100), (3, 8200), (9, 36)])
+def test_layernorm_bf16_rows_vs_oracle(pkg, ctx, n, size):
+    """bf16 rows and parameters, fp32 arithmetic: the oracle on the bf16-rounded inputs, output within one
+    bf16 unit in the last place (rtol 2^-8) plus 1e-2 near zero."""
+    gpu = pkg.gpu
+    rng = np.random.default_rng(size)
+    tb = lambda a: torch.from_numpy(a).to(torch.bfloat16).to(ctx.device)  # noqa: E731
+    x, gamma, beta = tb(rng.standard_normal((n, size)).astype(np.float32) * 2 + 0.5), \
+        tb(rng.standard_normal(size).astype(np.float32)), tb(rng.standard_normal(size).astype(np.float32))
+    out = torch.empty_like(x)
+    gpu.batch_begin(ctx)
+    gpu.layernorm(ctx, U.buf2d(pkg, ctx, x), gpu.GPUBuffer1D(buffer=gamma, shape=(size,), size=size),
+                  gpu.GPUBuffer1D(buffer=beta, shape=(size,), size=size), U.buf2d(pkg, ctx, out))
+    gpu.batch_commit(ctx)
+    want = T.layernorm(U.to_f32(x), U.to_f32(gamma), U.to_f32(beta))
+    np.testing.assert_allclose(U.to_f32(out), want, rtol=2.0 ** -8, atol=1e-2)
