@@ -53,6 +53,9 @@ WORKLOADS = {
                                    "GPUs, outputs all-gathered with NCCL"),
     "qkv_append": dict(B=64, H=32, D=128, T=256, layers=4, qkv=True,
                        desc="Q/K/V projection fused with the cache append: B=64 E=4096 (H=32 D=128) bf16, one layer per step"),
+    "decode_layer": dict(B=64, H=32, D=128, lo=512, hi=8192, layers=2, layer_step=True,
+                         desc="one decoder layer of a cached decode step (LN, QKV+append, attention, Wo, LN, MLP): "
+                              "B=64 E=4096 (H=32 D=128) bf16, len~U[512,8192] seed 0"),
     "prefill_small": dict(B=2, H=32, D=128, N=4096, prefill=True,
                           desc="causal prefill cut to 2 sequences (for profiler captures)"),
     "prefill": dict(B=8, H=32, D=128, N=4096, prefill=True,
@@ -198,7 +201,7 @@ def cpu_port_run(w, lens, steps, warmup, sample_seqs, log=None):
 def run_reference(args, w, rank):
     if rank != 0:
         return
-    if w.get("prefill") or w.get("qkv"):
+    if w.get("prefill") or w.get("qkv") or w.get("layer_step"):
         w = WORKLOADS["decode"]  # the CPU arm times the decode step, the headline workload
     lens = make_lengths(w, 0)
     steps = max(1, args.steps)
@@ -679,6 +682,134 @@ def run_qkv_append(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_decode_layer(args, w, rank, world):
+    """One whole decoder layer per step: layernorm, Q/K/V projection + append, cached attention, output
+    projection + residual, layernorm, MLP.  value = tokens/s through one layer; roofline = HBM over the bytes
+    the step must move (K/V rows attended + 12 E^2 weights + the small row buffers)."""
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pkg = __graft_entry__.import_package()
+    gpu = pkg.gpu
+    from llm_experiments_b200 import decode_layer
+
+    ctx = gpu.context_create(local_rank)
+    B, H, D, n_layers = w["B"], w["H"], w["D"], w["layers"]
+    E, T_max = H * D, w["hi"] + 8
+    dtype = torch.bfloat16
+    gen = torch.Generator(device=device).manual_seed(4000 + rank)
+    rnd = lambda shape, scale=1.0: (torch.randn(shape, generator=gen, device=device) * scale).to(dtype)  # noqa: E731
+    b2 = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    b1 = lambda t: gpu.GPUBuffer1D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+
+    def make_weights():
+        raw = dict(ln1_gamma=rnd((E,), 0.1) + 1, ln1_beta=rnd((E,), 0.1), wq=rnd((E, E), E ** -0.5), wk=rnd((E, E), E ** -0.5),
+                   wv=rnd((E, E), E ** -0.5), wo=rnd((E, E), E ** -0.5), ln2_gamma=rnd((E,), 0.1) + 1, ln2_beta=rnd((E,), 0.1),
+                   w1=rnd((E, 4 * E), E ** -0.5), b1=rnd((4 * E,), 0.1), w2=rnd((4 * E, E), (4 * E) ** -0.5), b2=rnd((E,), 0.1))
+        return decode_layer.DecoderLayerWeights(**{k: (b1(v) if v.dim() == 1 else b2(v)) for k, v in raw.items()})
+
+    weights = [make_weights() for _ in range(n_layers)]
+    lens = make_lengths(w, 0)
+    caches = []
+    for _ in range(n_layers):
+        c = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=dtype, layout="bhtd", ragged=True))
+        c.layers[0].k_cache.buffer.normal_(generator=gen)
+        c.layers[0].v_cache.buffer.normal_(generator=gen)
+        gpu.kv_cache_set_lengths(c, lens)
+        caches.append(c)
+    lens_dev, max_len = torch.from_numpy(lens.astype(np.int32)).to(device), int(lens.max())
+    x, y = rnd((B, E)), torch.empty((B, E), dtype=dtype, device=device)
+    xb, yb = b2(x), b2(y)
+    scratch = decode_layer.decoder_layer_scratch(ctx, B, E)
+    state = {"i": 0}
+
+    def step_device():
+        li = state["i"] % n_layers
+        state["i"] += 1
+        cache = caches[li]
+        cache.seq_lens.copy_(lens_dev)  # every step starts from the same lengths (256 bytes, device to device)
+        cache.current_len = max_len
+        gpu.batch_begin(ctx)
+        decode_layer.decoder_layer_step(ctx, cache, xb, weights[li], scratch, yb)
+        gpu.batch_commit(ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    steps, warm = args.steps, max(3, args.warmup)
+    for _ in range(warm):
+        step_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ms_step = timed(step_device, steps) / steps
+    xh, yh = x.cpu().pin_memory(), torch.empty_like(y, device="cpu").pin_memory()
+
+    def step_e2e():
+        gpu.gpu_buffer_2d_write(ctx, xh, xb)
+        step_device()
+        gpu.gpu_buffer_2d_read(ctx, yb, yh)
+
+    step_e2e()
+    ms_e2e = timed(step_e2e, steps) / steps
+    clocks = sampler.finish()
+    es = 2
+    kv_bytes = int((lens.astype(np.int64) + 1).sum()) * H * D * es * 2
+    weight_bytes = 12 * E * E * es
+    row_bytes = B * E * es * 14 + B * 4 * E * es * 2  # the [B, E] and [B, 4E] row buffers read / written between kernels
+    bytes_step = kv_bytes + weight_bytes + row_bytes
+    peak, kind = measured_hbm_peak()
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "tokens/s through one decoder layer (cached decode step)", "value": world * B / (ms_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, fp32 arithmetic",
+        "data": "synthetic",
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
+                   "l2": f"{n_layers} layers' caches and weights used in turn, far larger than L2",
+                   "parallelism": f"batch-sharded x{world}, no collective"},
+        "e2e": {"value": world * B / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": B * E * es, "d2h_bytes_per_step": B * E * es},
+        "gpu_launches": steps * 8, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "the layer's 8 kernels together", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": kind,
+                     "algorithmic_bytes_per_launch": bytes_step, "kv_bytes": kv_bytes, "weight_bytes": weight_bytes,
+                     "traffic": None},
+        "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of the split kernel per attended (token, head), from
 # an ncu capture of the 8-sequence case (`--workload decode_small`: 412.4 MB for
 # 24908 tokens x 32 heads; the algorithmic figure is 512 B).  Traffic grows in proportion to the
@@ -715,6 +846,9 @@ def main():
         return
     if w.get("qkv") and args.impl != "reference":
         run_qkv_append(args, w, rank, world)
+        return
+    if w.get("layer_step") and args.impl != "reference":
+        run_decode_layer(args, w, rank, world)
         return
     if args.impl == "reference":
         run_reference(args, w, rank)
