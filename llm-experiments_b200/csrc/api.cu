@@ -28,6 +28,7 @@ static Knob g_knobs[] = {
     {"decode_l2_keep", 0},  // 1 = K/V bulk copies use the default L2 policy instead of evict-first
     {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
     {"prefill_variant", 0},
+    {"matmul_splits", 0},  // ranges of input features per tile in b2kv_matmul_rows (0 = by shape)
 };
 
 int tune_get(const char* name) {

@@ -23,7 +23,15 @@
 //
 // The same kernel with one weight matrix [K, N] is the plain product of a decode step's rows with a
 // weight matrix (b2kv_matmul_rows: the attention output projection and the MLP), optionally with a
-// residual added before rounding.
+// bias, the reference's GELU and a residual applied before rounding.
+//
+// A matrix with few output features (N = E: 32 tiles at E = 4096) would keep only a few SMs streaming.
+// Its input features are then cut into `splits` ranges; the CTAs of a tile form a thread-block cluster,
+// each leaves its fp32 partial tile in its own shared memory (the ring is idle by then), and after a
+// cluster barrier every CTA adds up, in range order, a share of the sequences straight from its peers'
+// shared memory (distributed shared memory) and writes those outputs.  No partial goes to global
+// memory and the sum does not depend on timing.  (With enough tiles to fill the machine - the fused
+// Q/K/V form - splitting was measured slower and is not used.)
 #include "b2kv_common.cuh"
 #include "tc_ptx.cuh"
 #include "tma_map.cuh"
@@ -53,6 +61,7 @@ struct ProjShared {
     alignas(8) uint64_t full[kMaxStagesP], empty[kMaxStagesP];
     uint64_t done;
     uint32_t tmem_base;
+    int dumped;  // the epilogue left this CTA's partial tile in the ring
     long long row[kMaxBatch];  // element offset of every sequence's output row (-1: outside the cache), computed once
 };
 
@@ -69,6 +78,7 @@ struct ProjParams {
     const void* bias;                 // [E] added before the activation, or null
     int gelu;                         // x * sigmoid(1.702 x) after the bias (simple-llm/src/gpu/gpu_kernels.py:285-293)
     int stages;
+    int splits;  // CTAs per cluster = ranges of input features per tile
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -77,6 +87,23 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
             smem_u32(dst)),
         "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 32-bit word at the same shared-memory address in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t peer_smem_u32(const void* local, uint32_t rank) {
+    uint32_t addr, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
 }
 
 // Instruction descriptor: fp32 accumulate, bf16 operands, A MN-major, B K-major, M = 128, N = n.
@@ -91,10 +118,13 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     __shared__ ProjShared sm;
     uint8_t* const w_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int f0 = blockIdx.x * kFeat;  // first output feature, in the concatenation Wq | Wk | Wv
+    const int split = p.splits > 1 ? static_cast<int>(cluster_rank()) : 0;
+    const int f0 = (blockIdx.x / p.splits) * kFeat;  // first output feature, in the concatenation Wq | Wk | Wv
     const int which = f0 / p.E;         // 0 = Q, 1 = K, 2 = V
     const int c0 = f0 % p.E;            // first column inside that weight matrix
-    const int n_k = p.k_in / kKTile;
+    const int n_k_all = p.k_in / kKTile;  // this CTA's range of input-feature tiles
+    const int k_first = static_cast<int>(static_cast<long long>(n_k_all) * split / p.splits);
+    const int n_k = static_cast<int>(static_cast<long long>(n_k_all) * (split + 1) / p.splits) - k_first;
     const uint32_t x_span = static_cast<uint32_t>(p.Bn) * 128u;  // Bn rows of one 64-feature span
     uint8_t* const x_ring = w_ring + p.stages * kWBytes;
     const int n_st = p.stages;
@@ -106,6 +136,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.done, 1);
+        sm.dumped = 0;
         fence_mbar_init();
     }
     __syncthreads();  // barriers are initialised: the producer starts while the rest is set up
@@ -139,7 +170,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
                 const int st = i % n_st;
                 if (!mbar_wait(&sm.empty[st], ((i / n_st) & 1) ^ 1)) break;
                 mbar_arrive_expect_tx(&sm.full[st], stage_bytes);
-                const int k0 = i * kKTile;
+                const int k0 = (k_first + i) * kKTile;
                 // W tile: input features k0 .. +127 (rows), output features c0 .. c0+127 as two 64-wide boxes
                 tma_load_2d(w_ring + st * kWBytes, tw, &sm.full[st], c0, k0);
                 tma_load_2d(w_ring + st * kWBytes + kWHalf, tw, &sm.full[st], c0 + 64, k0);
@@ -189,6 +220,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
             const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
             const float bias = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : 0.f;
+            float* mine = reinterpret_cast<float*>(w_ring);  // partial tile [Bn][128] fp32 when the tile is split
             for (int nb = 0; nb < p.Bn; nb += 16) {
                 uint32_t v[16];
                 tmem_ld16(t_lane + nb, v);
@@ -196,7 +228,10 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const long long row = sm.row[nb + j];  // -1 past the batch and for positions outside the cache
-                    if (row >= 0) {
+                    if (row < 0) continue;
+                    if (p.splits > 1) {
+                        mine[(nb + j) * kFeat + m] = __uint_as_float(v[j]);
+                    } else {
                         float acc = __uint_as_float(v[j]) + bias;
                         if (p.gelu) acc = acc / (1.0f + __expf(-1.702f * acc));
                         if (res != nullptr) acc += __bfloat162float(res[row]);
@@ -204,6 +239,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
                     }
                 }
             }
+            if (m == 0) sm.dumped = 1;
         } else {
             report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
         }
@@ -214,6 +250,48 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(sm.tmem_base, kMaxBatch);
+    }
+    if (p.splits > 1) {
+        // every CTA of the tile has its partial in shared memory (or gave up: then nothing is written)
+        cluster_barrier();
+        if (warp < 4) {
+            const int m = threadIdx.x;
+            bool all = true;
+            for (int sp = 0; sp < p.splits; ++sp) all = all && peer_smem_u32(&sm.dumped, sp) != 0;
+            if (all) {
+                const float* mine = reinterpret_cast<const float*>(w_ring);
+                const int col = c0 + m;
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which == 0 ? p.q_out : (which == 1 ? p.k_cache : p.v_cache));
+                out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
+                const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
+                const float bias = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : 0.f;
+                // this CTA's share of the sequences: split, split + splits, ...; eight rows in flight
+                for (int b0 = split; b0 < p.B; b0 += 8 * p.splits) {
+                    float acc[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) acc[u] = bias;
+                    for (int sp = 0; sp < p.splits; ++sp) {  // fixed order
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int b = b0 + u * p.splits;
+                            if (b < p.B) acc[u] += __uint_as_float(peer_smem_u32(&mine[b * kFeat + m], sp));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int b = b0 + u * p.splits;
+                        if (b >= p.B) break;
+                        const long long row = sm.row[b];
+                        if (row < 0) continue;
+                        float a = acc[u];
+                        if (p.gelu) a = a / (1.0f + __expf(-1.702f * a));
+                        if (res != nullptr) a += __bfloat162float(res[row]);
+                        out[row] = __float2bfloat16_rn(a);
+                    }
+                }
+            }
+        }
+        cluster_barrier();  // nobody leaves while a peer still reads its shared memory
     }
 }
 
@@ -270,7 +348,7 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     proj::ProjParams p{q_out, k_cache, v_cache, seq_pos, dev_status, stride_b, stride_t, stride_h, pos, B, Bn, E, H, D, T_max,
-                       E, nullptr, nullptr, 0, stages};
+                       E, nullptr, nullptr, 0, stages, 1};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
@@ -295,13 +373,33 @@ extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* bias, 
     const int stage_bytes = proj::kWBytes + 2 * Bn * 128;
     const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
+    // few tiles: cut the input features so that about 128 CTAs stream (a power of two, at least two stages each)
+    const int tiles = N / proj::kFeat, n_k = K / proj::kKTile;
+    int splits = 1;
+    if (tune_get("matmul_splits") > 0) {
+        splits = std::min(std::min(tune_get("matmul_splits"), 8), n_k);
+    } else {
+        while (splits < 8 && tiles * splits * 2 <= 128 && n_k / (splits * 2) >= 2) splits *= 2;
+    }
     // one weight matrix: every tile is of kind 0 (plain rows of `out`); the cache fields are unused
-    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, bias, activation, stages};
+    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, bias, activation, stages, splits};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
     B2KV_CUDA_TRY(proj::configure_smem(dev, smem));
-    proj::qkv_append_kernel<<<N / proj::kFeat, proj::kProjThreads, smem, static_cast<cudaStream_t>(stream)>>>(tw, tw, tw, tx, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * splits);
+    cfg.blockDim = dim3(proj::kProjThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;  // the CTAs of one tile
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B2KV_CUDA_TRY(cudaLaunchKernelEx(&cfg, proj::qkv_append_kernel, tw, tw, tw, tx, p));
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
 }
