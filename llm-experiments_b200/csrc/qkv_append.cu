@@ -9,7 +9,7 @@
 //
 //   * the product is computed transposed, D[feature, sequence] = W^T x^T, so that the 128 rows of an MMA
 //     are output features (plentiful) and its columns are the sequences (few): one CTA per 128 output
-//     features of Wq | Wk | Wv.  A = a [64 k x 128 features] tile of W, which is an MN-major operand
+//     features of Wq | Wk | Wv.  A = a [128 k x 128 features] tile of W, which is an MN-major operand
 //     exactly as the weight matrix lies in memory; B = x, K-major.  (Handing the weights over transposed,
 //     so that A is K-major too, was measured and is no faster: the kernel is bound by what one SM pulls
 //     from L2 - 32 KB of weights plus 16 KB of x per stage in about 985 clocks - not by the MMAs);
@@ -32,6 +32,8 @@
 // shared memory (distributed shared memory) and writes those outputs.  No partial goes to global
 // memory and the sum does not depend on timing.  (With enough tiles to fill the machine - the fused
 // Q/K/V form - splitting was measured slower and is not used.)
+#include <algorithm>
+
 #include "b2kv_common.cuh"
 #include "tc_ptx.cuh"
 #include "tma_map.cuh"
