@@ -92,7 +92,7 @@ def test_qkv_project_append_checks(pkg, ctx):
 
 
 @pytest.mark.parametrize("M,K,N,with_residual", [(64, 1024, 512, False), (5, 128, 256, True), (128, 512, 128, True),
-                                                 (1, 4096, 1024, False), (33, 256, 1280, True)])
+                                                 (1, 4096, 1024, False), (33, 256, 1280, True), (8, 512, 8192, True)])
 def test_matmul_rows_vs_oracle(pkg, ctx, M, K, N, with_residual):
     gpu = pkg.gpu
     A = _bf16(ctx, (M, K), 11)
@@ -122,6 +122,25 @@ def test_matmul_with_bias_gelu_and_residual_like_the_mlp(pkg, ctx):
     gpu.batch_commit(ctx)
     z = U.to_f32(A).astype(np.float64) @ U.to_f32(W).astype(np.float64) + U.to_f32(bias)
     want = z / (1.0 + np.exp(-1.702 * z)) + U.to_f32(R)
+    np.testing.assert_allclose(U.to_f32(C), want.astype(np.float32), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5])
+def test_matmul_rows_with_forced_input_ranges(pkg, ctx, splits):
+    """Every way of cutting the input features over a thread-block cluster gives the same product."""
+    gpu = pkg.gpu
+    M, K, N = 16, 768, 256
+    A, W, R = _bf16(ctx, (M, K), 31), _bf16(ctx, (K, N), 32, scale=K ** -0.5), _bf16(ctx, (M, N), 33)
+    C = torch.zeros((M, N), dtype=torch.bfloat16, device=ctx.device)
+    try:
+        pkg._native.tune("matmul_splits", splits)
+        gpu.batch_begin(ctx)
+        gpu.matmul(ctx, U.buf2d(pkg, ctx, A), U.buf2d(pkg, ctx, W), U.buf2d(pkg, ctx, C), residual=U.buf2d(pkg, ctx, R))
+        gpu.batch_commit(ctx)
+        torch.cuda.synchronize()
+    finally:
+        pkg._native.tune("matmul_splits", 0)
+    want = U.to_f32(A).astype(np.float64) @ U.to_f32(W).astype(np.float64) + U.to_f32(R)
     np.testing.assert_allclose(U.to_f32(C), want.astype(np.float32), rtol=RTOL, atol=ATOL)
 
 
