@@ -58,3 +58,48 @@ def test_decoder_layer_step_vs_oracle(pkg, B, H, D, ragged):
         assert np.array_equal(cache.seq_lens.cpu().numpy(), lens + 1)
     else:
         assert cache.current_len == 12
+
+
+def test_two_layers_over_several_steps_track_the_oracle(pkg):
+    """Two stacked layers (one cache object each) over six decode steps: the caches grow by one row per step and
+    layer, and every step's output stays within the layer tolerance of the oracle that is fed the GPU's own
+    previous rows (so that rounding differences do not compound across steps)."""
+    from llm_experiments_b200 import decode_layer
+
+    gpu = pkg.gpu
+    ctx = U.make_ctx(pkg)
+    B, H, D, T_max, n_layers, n_steps = 4, 2, 64, 16, 2, 6
+    E = H * D
+    g = torch.Generator().manual_seed(7)
+    rnd = lambda shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(ctx.device)  # noqa: E731
+    b2 = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    b1 = lambda t: gpu.GPUBuffer1D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    raws, weights, caches = [], [], []
+    for _ in range(n_layers):
+        raw = dict(ln1_gamma=rnd((E,), 0.2) + 1, ln1_beta=rnd((E,), 0.1), wq=rnd((E, E), E ** -0.5), wk=rnd((E, E), E ** -0.5),
+                   wv=rnd((E, E), E ** -0.5), wo=rnd((E, E), E ** -0.5), ln2_gamma=rnd((E,), 0.2) + 1, ln2_beta=rnd((E,), 0.1),
+                   w1=rnd((E, 4 * E), E ** -0.5), b1=rnd((4 * E,), 0.1), w2=rnd((4 * E, E), (4 * E) ** -0.5), b2=rnd((E,), 0.1))
+        raws.append({k: U.to_f32(v) for k, v in raw.items()})
+        weights.append(decode_layer.DecoderLayerWeights(**{k: (b1(v) if v.dim() == 1 else b2(v)) for k, v in raw.items()}))
+        caches.append(gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H,
+                                                                 head_dim=D, dtype=torch.bfloat16, layout="bhtd")))
+    scratch = decode_layer.decoder_layer_scratch(ctx, B, E)
+    bufs = [torch.empty((B, E), dtype=torch.bfloat16, device=ctx.device) for _ in range(n_layers + 1)]
+    for step in range(n_steps):
+        bufs[0].copy_(rnd((B, E)))
+        before = [(U.to_f32(U.logical_view(c, c.layers[0], "k")).reshape(B, T_max, E),
+                   U.to_f32(U.logical_view(c, c.layers[0], "v")).reshape(B, T_max, E)) for c in caches]
+        gpu.batch_begin(ctx)
+        for li in range(n_layers):
+            decode_layer.decoder_layer_step(ctx, caches[li], b2(bufs[li]), weights[li], scratch, b2(bufs[li + 1]))
+        gpu.batch_commit(ctx)
+        torch.cuda.synchronize()
+        lens = np.full(B, step, dtype=np.int32)
+        for li in range(n_layers):
+            assert caches[li].current_len == step + 1
+            want_y, want_k, _ = decode_layer_oracle.decoder_layer_step(U.to_f32(bufs[li]), raws[li], list(before[li][0]),
+                                                                        list(before[li][1]), lens, H)
+            np.testing.assert_allclose(U.to_f32(bufs[li + 1]), want_y, rtol=2.0 ** -6, atol=3e-2)
+            k_now = U.to_f32(U.logical_view(caches[li], caches[li].layers[0], "k")).reshape(B, T_max, E)
+            np.testing.assert_allclose(k_now[:, step], want_k, rtol=2.0 ** -7, atol=1e-2)
+            assert float(np.abs(k_now[:, step + 1:]).sum()) == 0.0  # rows after the new one are still untouched
