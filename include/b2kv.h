@@ -262,6 +262,19 @@ int b2kv_matmul_rows(const void* x, const void* w, const void* bias, const void*
                      int activation, int dtype, void* stream);
 
 /*
+ * out = act(a @ w + bias) + residual for any number of rows: a [M, K], w [K, N] row-major ([in, out], as the
+ * reference stores its weights), bias [N] (nullable), residual (nullable) and out [M, N]; activation as in
+ * b2kv_matmul_rows; bf16 with fp32 accumulation, K and N multiples of 8.  Replaces the reference's matmul
+ * dispatch (simple-llm/src/gpu/gpu_pass_forward.py:35-82, C = A @ B; kernel src/gpu/gpu_kernels.py:10-134) for
+ * the prompt-side projections either side of flash_attention (src/wgpu_backend.py:812-930), with the bias_add
+ * (:211-248), gelu (:179-209) and residual_add (:250-283) dispatches that follow it there.  A persistent
+ * tensor-core kernel over 128 x 256 output tiles; for at most 128 rows b2kv_matmul_rows streams the weights
+ * faster.
+ */
+int b2kv_matmul(const void* a, const void* w, const void* bias, const void* residual, void* out, int M, int K, int N,
+                int activation, int dtype, void* stream);
+
+/*
  * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,

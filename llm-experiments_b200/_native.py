@@ -61,6 +61,7 @@ SIGNATURES = {
     "b2kv_argmax": (_i, [_vp, _vp, _i, _i, _vp]),
     "b2kv_qkv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_matmul_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b2kv_matmul": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "b2kv_tune": (_i, [ctypes.c_char_p, _i]),
 }
 

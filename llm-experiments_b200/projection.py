@@ -21,8 +21,10 @@ from .types import GPUBuffer2D, GPUContext, KVCache
 def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, residual: GPUBuffer2D = None,
            bias=None, activation: str = None) -> None:
     """``C = A @ B`` with the reference's argument order and shape check
-    (simple-llm/src/gpu/gpu_pass_forward.py:35-82), for the shapes of a cached decode step: bfloat16,
-    at most 128 rows in ``A``, inner and outer dimensions multiples of 128.  Extensions that fold the
+    (simple-llm/src/gpu/gpu_pass_forward.py:35-82), bfloat16, inner and outer dimensions multiples of 8.
+    The rows of a cached decode step (at most 128 rows in ``A``, dimensions multiples of 128) go to the
+    weight-streaming kernel, every other shape (the prompt-side projections) to the tiled tensor-core
+    GEMM.  Extensions that fold the
     dispatches which follow a matmul in the reference's block (src/wgpu_backend.py:857-930) into
     it: ``bias`` (a ``GPUBuffer1D`` of N values, ``bias_add``), ``activation="gelu"``
     (``x * sigmoid(1.702 x)``, ``gelu``) and ``residual`` (``residual_add``), applied in that order:
@@ -45,13 +47,15 @@ def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, resi
     bufs = [A, B, C] + [t for t in (residual, bias) if t is not None]
     if any(t.buffer.dtype != torch.bfloat16 for t in bufs):
         raise ValueError("matmul takes bfloat16 buffers")
-    if M > 128 or K % 128 != 0 or N % 128 != 0:
-        raise ValueError("matmul covers decode-step shapes: at most 128 rows, K and N multiples of 128")
+    if K % 8 != 0 or N % 8 != 0:
+        raise ValueError("matmul needs inner and outer dimensions that are multiples of 8 (16-byte rows)")
+    # the rows of a decode step stream the weights once (b2kv_matmul_rows); everything else is a tiled GEMM
+    rows_kernel = M <= 128 and K % 128 == 0 and N % 128 == 0
+    fn = _native.lib.b2kv_matmul_rows if rows_kernel else _native.lib.b2kv_matmul
     stream = batch_op_begin(ctx)
-    rc = _native.lib.b2kv_matmul_rows(A.buffer.data_ptr(), B.buffer.data_ptr(),
-                                      None if bias is None else bias.buffer.data_ptr(),
-                                      None if residual is None else residual.buffer.data_ptr(), C.buffer.data_ptr(),
-                                      M, K, N, 1 if activation == "gelu" else 0, dtype_code(torch.bfloat16), stream)
+    rc = fn(A.buffer.data_ptr(), B.buffer.data_ptr(), None if bias is None else bias.buffer.data_ptr(),
+            None if residual is None else residual.buffer.data_ptr(), C.buffer.data_ptr(), M, K, N,
+            1 if activation == "gelu" else 0, dtype_code(torch.bfloat16), stream)
     _native.check(rc)
 
 

@@ -154,6 +154,40 @@ def test_matmul_checks(pkg, ctx):
         gpu.matmul(ctx, mk(4, 128), mk(128, 128), mk(4, 256))
     with pytest.raises(ValueError, match="bfloat16"):
         gpu.matmul(ctx, mk(4, 128, torch.float32), mk(128, 128), mk(4, 128))
-    with pytest.raises(ValueError, match="decode-step shapes"):
-        gpu.matmul(ctx, mk(4, 64), mk(64, 128), mk(4, 128))
+    with pytest.raises(ValueError, match="multiples of 8"):
+        gpu.matmul(ctx, mk(4, 60), mk(60, 128), mk(4, 128))
     gpu.batch_commit(ctx)
+
+
+@pytest.mark.parametrize("M,K,N,epilogue", [
+    (129, 128, 128, "none"),       # one row past a tile: the second row tile is almost empty
+    (256, 64, 256, "none"),        # a single stage per tile
+    (1000, 520, 776, "all"),       # ragged rows, input features and columns (zero-filled edges, masked stores)
+    (64, 72, 40, "residual"),      # a decode-sized matrix whose dimensions the rows kernel does not take
+    (4096, 1024, 1024, "all"),     # several tiles per CTA: both accumulators, ring wrap-around
+    (2048, 512, 4096, "bias"),     # more column tiles than a band has row tiles
+    (3000, 256, 264, "gelu"),      # a last column tile of 8 columns
+])
+def test_matmul_tiled_gemm_vs_oracle(pkg, ctx, M, K, N, epilogue):
+    """The tiled tensor-core GEMM behind ``matmul`` for more rows than a decode step has, with each
+    epilogue, against a float64 product."""
+    gpu = pkg.gpu
+    A, W = _bf16(ctx, (M, K), 41), _bf16(ctx, (K, N), 42, scale=K ** -0.5)
+    bias = _bf16(ctx, (N,), 43) if epilogue in ("all", "bias") else None
+    R = _bf16(ctx, (M, N), 44) if epilogue in ("all", "residual") else None
+    act = "gelu" if epilogue in ("all", "gelu") else None
+    C = torch.full((M + 1, N), 7.0, dtype=torch.bfloat16, device=ctx.device)  # one guard row behind the output
+    Cb = U.buf2d(pkg, ctx, C[:M])
+    gpu.batch_begin(ctx)
+    gpu.matmul(ctx, U.buf2d(pkg, ctx, A), U.buf2d(pkg, ctx, W), Cb, residual=None if R is None else U.buf2d(pkg, ctx, R),
+               bias=None if bias is None else gpu.GPUBuffer1D(buffer=bias, shape=(N,), size=N), activation=act)
+    gpu.batch_commit(ctx)
+    z = U.to_f32(A).astype(np.float64) @ U.to_f32(W).astype(np.float64)
+    if bias is not None:
+        z = z + U.to_f32(bias)
+    if act:
+        z = z / (1.0 + np.exp(-1.702 * z))
+    if R is not None:
+        z = z + U.to_f32(R)
+    np.testing.assert_allclose(U.to_f32(C[:M]), z.astype(np.float32), rtol=RTOL, atol=ATOL)
+    assert bool((C[M] == 7.0).all())  # nothing written past the last row
