@@ -56,6 +56,11 @@ WORKLOADS = {
     "decode_layer": dict(B=64, H=32, D=128, lo=512, hi=8192, layers=2, layer_step=True,
                          desc="one decoder layer of a cached decode step (LN, QKV+append, attention, Wo, LN, MLP): "
                               "B=64 E=4096 (H=32 D=128) bf16, len~U[512,8192] seed 0"),
+    "prefill_layer": dict(B=8, H=32, D=128, N=4096, layers=2, prompt_layer=True,
+                          desc="one decoder layer over a whole prompt (LN, Q/K/V GEMMs, causal attention + cache write, Wo, "
+                               "LN, MLP): B=8 N=4096 E=4096 (H=32 D=128) bf16"),
+    "prefill_layer_small": dict(B=1, H=32, D=128, N=4096, layers=2, prompt_layer=True,
+                                desc="the prompt-side layer cut to one sequence (for profiler captures)"),
     "prefill_small": dict(B=2, H=32, D=128, N=4096, prefill=True,
                           desc="causal prefill cut to 2 sequences (for profiler captures)"),
     "prefill": dict(B=8, H=32, D=128, N=4096, prefill=True,
@@ -810,6 +815,128 @@ def run_decode_layer(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_prompt_layer(args, w, rank, world):
+    """One whole decoder layer over a prompt per step: layernorm, three projection GEMMs, causal attention
+    fused with the cache write, output projection + residual, layernorm, MLP.  value = prompt tokens/s
+    through one layer; roofline = tensor, over the layer's matmul and attention flops."""
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pkg = __graft_entry__.import_package()
+    gpu = pkg.gpu
+    from llm_experiments_b200 import decode_layer
+
+    ctx = gpu.context_create(local_rank)
+    ctx.config.flash_attn_max_head_dim = 128
+    B, H, D, N, n_layers = w["B"], w["H"], w["D"], w["N"], w["layers"]
+    E, rows = H * D, B * N
+    dtype = torch.bfloat16
+    gen = torch.Generator(device=device).manual_seed(5000 + rank)
+    rnd = lambda shape, scale=1.0: (torch.randn(shape, generator=gen, device=device) * scale).to(dtype)  # noqa: E731
+    b2 = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    b1 = lambda t: gpu.GPUBuffer1D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+
+    def make_weights():
+        raw = dict(ln1_gamma=rnd((E,), 0.1) + 1, ln1_beta=rnd((E,), 0.1), wq=rnd((E, E), E ** -0.5), wk=rnd((E, E), E ** -0.5),
+                   wv=rnd((E, E), E ** -0.5), wo=rnd((E, E), E ** -0.5), ln2_gamma=rnd((E,), 0.1) + 1, ln2_beta=rnd((E,), 0.1),
+                   w1=rnd((E, 4 * E), E ** -0.5), b1=rnd((4 * E,), 0.1), w2=rnd((4 * E, E), (4 * E) ** -0.5), b2=rnd((E,), 0.1))
+        return decode_layer.DecoderLayerWeights(**{k: (b1(v) if v.dim() == 1 else b2(v)) for k, v in raw.items()})
+
+    weights = [make_weights() for _ in range(n_layers)]
+    caches = [gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=N, n_layers=1, n_heads=H, head_dim=D,
+                                                         dtype=dtype, layout="bhtd")) for _ in range(n_layers)]
+    x, y = rnd((rows, E)), torch.empty((rows, E), dtype=dtype, device=device)
+    xb, yb = b2(x), b2(y)
+    scratch = decode_layer.prompt_layer_scratch(ctx, rows, E)
+    state = {"i": 0}
+
+    def step_device():
+        li = state["i"] % n_layers
+        state["i"] += 1
+        gpu.batch_begin(ctx)
+        decode_layer.prompt_layer_step(ctx, caches[li], xb, weights[li], scratch, yb, B, N)
+        gpu.batch_commit(ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    steps, warm = min(args.steps, 50), max(3, args.warmup)
+    for _ in range(warm):
+        step_device()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    ms_step = timed(step_device, steps) / steps
+    xh, yh = x.cpu().pin_memory(), torch.empty_like(y, device="cpu").pin_memory()
+
+    def step_e2e():
+        gpu.gpu_buffer_2d_write(ctx, xh, xb)
+        step_device()
+        gpu.gpu_buffer_2d_read(ctx, yb, yh)
+
+    step_e2e()
+    e2e_steps = max(2, min(steps, 5))
+    ms_e2e = timed(step_e2e, e2e_steps) / e2e_steps
+    clocks = sampler.finish()
+    es = 2
+    gemm_flops = 2.0 * rows * E * E * 12  # Q, K, V, Wo (4 E^2) + the MLP (8 E^2)
+    attn_flops = 4.0 * B * H * D * N * (N + 1) / 2
+    flops = gemm_flops + attn_flops
+    sustained, burst, kind = measured_tensor_peak()
+    achieved = flops / (ms_step * 1e-3) / 1e12
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "prompt tokens/s through one decoder layer", "value": world * rows / (ms_step * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B, "seq_len": N,
+                   "l2": f"{n_layers} layers' weights used in turn; activations ({rows * E * es / 1e6:.0f} MB per buffer) "
+                         "larger than L2",
+                   "parallelism": f"batch-sharded x{world}, no collective"},
+        "e2e": {"value": world * rows / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": rows * E * es, "d2h_bytes_per_step": rows * E * es},
+        "gpu_launches": steps * 9, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "the layer's 9 kernels together (6 gemm_tc_kernel, prefill_tc_kernel, "
+                                                  "2 layernorm)",
+                     "achieved": achieved, "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained,
+                     "frac_of_burst": achieved / burst,
+                     "peak_kind": f"{kind} (sustained cuBLAS bf16; the layer is timed in a long loop)",
+                     "algorithmic_flops_per_launch": flops, "gemm_flops": gemm_flops, "attention_flops": attn_flops,
+                     "traffic": None},
+        "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of the split kernel per attended (token, head), from
 # an ncu capture of the 8-sequence case (`--workload decode_small`: 412.4 MB for
 # 24908 tokens x 32 heads; the algorithmic figure is 512 B).  Traffic grows in proportion to the
@@ -849,6 +976,9 @@ def main():
         return
     if w.get("layer_step") and args.impl != "reference":
         run_decode_layer(args, w, rank, world)
+        return
+    if w.get("prompt_layer") and args.impl != "reference":
+        run_prompt_layer(args, w, rank, world)
         return
     if args.impl == "reference":
         run_reference(args, w, rank)

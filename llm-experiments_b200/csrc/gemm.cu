@@ -7,8 +7,8 @@
 // kernel in qkv_append.cu instead.
 //
 //   * persistent grid, one CTA per SM; a CTA walks output tiles of 128 rows x 256 columns.  Tiles are
-//     ordered in bands of 8 row tiles x all column tiles, so that the CTAs running together share a few
-//     row tiles of A and the whole of W out of L2;
+//     ordered in blocks of 8 row tiles x 16 column tiles (about one wave of CTAs), so that the CTAs running
+//     together share a few row tiles of A and 4096 columns of W out of L2;
 //   * warp 0 streams A (128 rows x 64 input features, K-major) and W (64 input features x 256 columns, the
 //     matrix as it lies in memory = an MN-major operand, four 64-column boxes) with TMA tiled loads, 128-byte
 //     swizzle, into a 4-stage ring of 48 KB stages that complete on mbarriers;
@@ -41,7 +41,8 @@ constexpr int kWBytes = (kBN / 64) * kWSpanBytes;  // 32 KB
 constexpr int kStageBytes = kABytes + kWBytes;
 constexpr int kThreads = 192;  // warp 0 producer, warp 1 MMA issuer, warps 2-5 epilogue
 constexpr int kTmemCols = 512;  // two accumulators of 256 columns
-constexpr int kBandRows = 8;    // row tiles per band of the tile order
+constexpr int kBandRows = 8;    // row tiles and
+constexpr int kBandCols = 16;   // column tiles per block of the tile order (128 tiles: about one wave of CTAs)
 
 struct GemmParams {
     const __nv_bfloat16* bias;      // [N] or null
@@ -68,15 +69,21 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         : "memory");
 }
 
-// Tile t of the order described above -> (row tile, column tile).
+// Tile t of the order described above -> (row tile, column tile): column bands outermost, then row bands,
+// then the tiles of a block with the row tile running fastest.
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm, int& tn) {
-    const int band_tiles = kBandRows * p.tiles_n;
-    const int band = t / band_tiles;
-    const int first = band * kBandRows;
-    const int rows_here = min(kBandRows, p.tiles_m - first);
-    const int within = t - band * band_tiles;
-    tm = first + within % rows_here;
-    tn = within / rows_here;
+    const int cband_tiles = p.tiles_m * kBandCols;
+    const int cband = t / cband_tiles;  // only the last column band can be narrower, and nothing follows it
+    const int first_col = cband * kBandCols;
+    const int cols_here = min(kBandCols, p.tiles_n - first_col);
+    const int in_cband = t - cband * cband_tiles;
+    const int block_tiles = kBandRows * cols_here;
+    const int rband = in_cband / block_tiles;
+    const int first_row = rband * kBandRows;
+    const int rows_here = min(kBandRows, p.tiles_m - first_row);
+    const int within = in_cband - rband * block_tiles;
+    tm = first_row + within % rows_here;
+    tn = first_col + within / rows_here;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)

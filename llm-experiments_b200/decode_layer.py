@@ -24,6 +24,7 @@ from typing import Optional
 
 import torch
 
+from .attention import flash_attention
 from .kv_cache import attention_with_kv_cache
 from .projection import matmul, qkv_project_append
 from .step_tail import layernorm
@@ -79,6 +80,45 @@ def decoder_layer_step(ctx: GPUContext, cache: KVCache, x: GPUBuffer2D, w: Decod
     layernorm(ctx, x, w.ln1_gamma, w.ln1_beta, s.h)
     qkv_project_append(ctx, cache, 0, s.h, w.wq, w.wk, w.wv, s.q)
     attention_with_kv_cache(ctx, cache, 0, s.q, s.a)
+    matmul(ctx, s.a, w.wo, s.x2, residual=x)
+    layernorm(ctx, s.x2, w.ln2_gamma, w.ln2_beta, s.h)
+    matmul(ctx, s.h, w.w1, s.m, bias=w.b1, activation="gelu")
+    matmul(ctx, s.m, w.w2, y, bias=w.b2, residual=s.x2)
+
+
+@dataclass
+class PromptLayerScratch:
+    """Intermediate rows of a prompt-side layer pass (``batch_size * seq_len`` rows each)."""
+
+    h: GPUBuffer2D     # normalised rows (both layer norms)
+    q: GPUBuffer2D
+    k: GPUBuffer2D
+    v: GPUBuffer2D
+    a: GPUBuffer2D     # attention output
+    x2: GPUBuffer2D
+    m: GPUBuffer2D     # MLP hidden rows [rows, 4E]
+
+
+def prompt_layer_scratch(ctx: GPUContext, rows: int, embedding_dim: int, hidden_dim: Optional[int] = None) -> PromptLayerScratch:
+    hidden_dim = hidden_dim or 4 * embedding_dim
+    mk = lambda c: _buf(ctx, rows, c)  # noqa: E731
+    return PromptLayerScratch(h=mk(embedding_dim), q=mk(embedding_dim), k=mk(embedding_dim), v=mk(embedding_dim),
+                              a=mk(embedding_dim), x2=mk(embedding_dim), m=mk(hidden_dim))
+
+
+def prompt_layer_step(ctx: GPUContext, cache: KVCache, x: GPUBuffer2D, w: DecoderLayerWeights, s: PromptLayerScratch,
+                      y: GPUBuffer2D, batch_size: int, seq_len: int) -> None:
+    """The same layer for a whole prompt: ``x`` and ``y`` are ``[batch_size * seq_len, E]``.  The reference's
+    block as it stands (simple-llm/src/wgpu_backend.py:794-935: three projections, causal
+    ``flash_attention``, output projection, MLP), with the prompt's K / V rows written into ``cache``
+    (layer 0 of that cache object; its length becomes ``seq_len``) by the attention kernel.  Nine
+    operations are recorded; the projections run on the tiled tensor-core GEMM."""
+    layernorm(ctx, x, w.ln1_gamma, w.ln1_beta, s.h)
+    matmul(ctx, s.h, w.wq, s.q)
+    matmul(ctx, s.h, w.wk, s.k)
+    matmul(ctx, s.h, w.wv, s.v)
+    flash_attention(ctx, s.q, s.k, s.v, s.a, None, None, batch_size, seq_len, cache.n_heads, cache.head_dim,
+                    cache=cache, layer_idx=0)
     matmul(ctx, s.a, w.wo, s.x2, residual=x)
     layernorm(ctx, s.x2, w.ln2_gamma, w.ln2_beta, s.h)
     matmul(ctx, s.h, w.w1, s.m, bias=w.b1, activation="gelu")

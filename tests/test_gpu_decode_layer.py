@@ -103,3 +103,57 @@ def test_two_layers_over_several_steps_track_the_oracle(pkg):
             k_now = U.to_f32(U.logical_view(caches[li], caches[li].layers[0], "k")).reshape(B, T_max, E)
             np.testing.assert_allclose(k_now[:, step], want_k, rtol=2.0 ** -7, atol=1e-2)
             assert float(np.abs(k_now[:, step + 1:]).sum()) == 0.0  # rows after the new one are still untouched
+
+
+@pytest.mark.parametrize("B,N,H,D", [(2, 256, 2, 128), (3, 160, 4, 64)])
+def test_prompt_layer_step_vs_oracle_then_decode_continues(pkg, B, N, H, D):
+    """The same layer over a whole prompt (projections on the tiled GEMM, causal attention fused with the
+    cache write), then one cached decode step on top of the prefilled cache: both against the oracle."""
+    from llm_experiments_b200 import decode_layer
+
+    gpu = pkg.gpu
+    ctx = U.make_ctx(pkg)
+    ctx.config.flash_attn_max_head_dim = 128
+    E, T_max = H * D, N + 16
+    g = torch.Generator().manual_seed(100 + B)
+    rnd = lambda shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(ctx.device)  # noqa: E731
+    b2 = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    b1 = lambda t: gpu.GPUBuffer1D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    raw = dict(ln1_gamma=rnd((E,), 0.2) + 1, ln1_beta=rnd((E,), 0.1), wq=rnd((E, E), E ** -0.5), wk=rnd((E, E), E ** -0.5),
+               wv=rnd((E, E), E ** -0.5), wo=rnd((E, E), E ** -0.5), ln2_gamma=rnd((E,), 0.2) + 1, ln2_beta=rnd((E,), 0.1),
+               w1=rnd((E, 4 * E), E ** -0.5), b1=rnd((4 * E,), 0.1), w2=rnd((4 * E, E), (4 * E) ** -0.5), b2=rnd((E,), 0.1))
+    w = decode_layer.DecoderLayerWeights(**{k: (b1(v) if v.dim() == 1 else b2(v)) for k, v in raw.items()})
+    wf = {k: U.to_f32(v) for k, v in raw.items()}
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=torch.bfloat16, layout="bhtd"))
+    x = rnd((B * N, E))
+    y = torch.empty_like(x)
+    scratch = decode_layer.prompt_layer_scratch(ctx, B * N, E)
+    gpu.batch_begin(ctx)
+    decode_layer.prompt_layer_step(ctx, cache, b2(x), w, scratch, b2(y), B, N)
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    want_y, want_k, want_v = decode_layer_oracle.prompt_layer_step(U.to_f32(x), wf, B, N, H)
+    np.testing.assert_allclose(U.to_f32(y), want_y, rtol=2.0 ** -6, atol=3e-2)
+    assert cache.current_len == N
+    layer = cache.layers[0]
+    k_rows = U.logical_view(cache, layer, "k")[:, :N].reshape(B * N, E)
+    v_rows = U.logical_view(cache, layer, "v")[:, :N].reshape(B * N, E)
+    # the cache holds exactly the projected rows (bit-exact copy), which match the oracle's projection
+    assert torch.equal(k_rows, scratch.k.buffer) and torch.equal(v_rows, scratch.v.buffer)
+    np.testing.assert_allclose(U.to_f32(k_rows), want_k, rtol=2.0 ** -7, atol=1e-2)
+    np.testing.assert_allclose(U.to_f32(v_rows), want_v, rtol=2.0 ** -7, atol=1e-2)
+    # one decode step over the prefilled cache
+    k_before = U.to_f32(U.logical_view(cache, layer, "k")).reshape(B, T_max, E)
+    v_before = U.to_f32(U.logical_view(cache, layer, "v")).reshape(B, T_max, E)
+    x1 = rnd((B, E))
+    y1 = torch.empty_like(x1)
+    dscratch = decode_layer.decoder_layer_scratch(ctx, B, E)
+    gpu.batch_begin(ctx)
+    decode_layer.decoder_layer_step(ctx, cache, b2(x1), w, dscratch, b2(y1))
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    want_y1, _, _ = decode_layer_oracle.decoder_layer_step(U.to_f32(x1), wf, list(k_before), list(v_before),
+                                                           np.full(B, N, dtype=np.int32), H)
+    np.testing.assert_allclose(U.to_f32(y1), want_y1, rtol=2.0 ** -6, atol=3e-2)
+    assert cache.current_len == N + 1

@@ -146,3 +146,23 @@ def test_decode_zero_length_sequence_is_zero():
     q = rng.standard_normal((B, H * D)).astype(np.float32)
     out = c_oracle.decode(q, k, v, np.array([0, 3], dtype=np.int32), B, H, D, (T * H * D, H * D, D))
     assert np.all(out[0] == 0) and np.any(out[1] != 0)
+
+
+def test_prompt_layer_oracle_agrees_with_the_decode_layer_oracle_on_the_last_token():
+    """Two restatements of the reference block (whole prompt with a causal mask; one new token over cached
+    rows) must give the same row for the last token of every sequence."""
+    from oracle import decode_layer_oracle as o
+
+    E, H, B, N = 64, 2, 2, 24
+    rng = np.random.default_rng(0)
+    r = lambda *s: o.bf16_round(rng.standard_normal(s).astype(np.float32) * 0.2)  # noqa: E731
+    w = dict(ln1_gamma=r(E) + 1, ln1_beta=r(E), wq=r(E, E), wk=r(E, E), wv=r(E, E), wo=r(E, E), ln2_gamma=r(E) + 1,
+             ln2_beta=r(E), w1=r(E, 4 * E), b1=r(4 * E), w2=r(4 * E, E), b2=r(E))
+    x = r(B * N, E)
+    y, k, v = o.prompt_layer_step(x, w, B, N, H)
+    last = [N - 1, 2 * N - 1]
+    ks = [k[b * N:(b + 1) * N] for b in range(B)]
+    vs = [v[b * N:(b + 1) * N] for b in range(B)]
+    y_last, k_new, _ = o.decoder_layer_step(x[last], w, ks, vs, np.full(B, N - 1), H)
+    np.testing.assert_allclose(y_last, y[last], rtol=0, atol=1e-6)
+    np.testing.assert_array_equal(k_new, k[last])
