@@ -86,6 +86,8 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm,
     tn = first_col + within / rows_here;
 }
 
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_addr, int grow, int col_base);
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -184,54 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             ok = mbar_wait(&sm.acc_full[buf], (local >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            const int grow = tm * kBM + row;
-            const size_t row_off = static_cast<size_t>(grow) * p.N;
-#pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                const int col0 = tn * kBN + c * 32;
-                if (col0 >= p.N) break;  // the same for every thread of the CTA
-                uint32_t acc[32];
-                tmem_ld32(tmem + lane_base + buf * kBN + c * 32, acc);
-                tmem_wait_ld();
-                if (grow < p.M) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const int col = col0 + v * 8;
-                        if (col >= p.N) break;
-                        float z[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) z[i] = __uint_as_float(acc[v * 8 + i]);
-                        if (p.bias != nullptr) {
-                            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
-                            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                z[2 * i] += __uint_as_float(bw[i] << 16);
-                                z[2 * i + 1] += __uint_as_float(bw[i] & 0xffff0000u);
-                            }
-                        }
-                        if (p.gelu) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) z[i] = z[i] / (1.0f + __expf(-1.702f * z[i]));
-                        }
-                        if (p.residual != nullptr) {
-                            const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + row_off + col);
-                            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                z[2 * i] += __uint_as_float(rw[i] << 16);
-                                z[2 * i + 1] += __uint_as_float(rw[i] & 0xffff0000u);
-                            }
-                        }
-                        uint4 w;
-                        w.x = pack_bf16(z[0], z[1]);
-                        w.y = pack_bf16(z[2], z[3]);
-                        w.z = pack_bf16(z[4], z[5]);
-                        w.w = pack_bf16(z[6], z[7]);
-                        *reinterpret_cast<uint4*>(p.out + row_off + col) = w;
-                    }
-                }
-            }
+            epilogue_rows(p, tmem + lane_base + buf * kBN, tm * kBM + row, tn * kBN);
             // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
             tc_fence_before();
             __syncwarp();
@@ -246,6 +201,260 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// CTA-pair form (tcgen05 cta_group::2).  A cluster of two CTAs owns an output tile of 256 rows x 256
+// columns: CTA r holds rows [128 r, 128 r + 128) of A and columns [128 r, 128 r + 128) of W, and every MMA
+// is M = 256 over the pair, so each SM writes (TMA) and reads (MMA) 16 KB of A + 16 KB of W per 64 input
+// features instead of 16 + 32: the one-CTA form's shared-memory port carries 96 B/clk of operand reads plus
+// the same again in TMA writes, which holds its tensor pipe at 80 %.  The copies of both CTAs complete on
+// the leader's barriers, one thread of the leader issues the MMAs and commits to the barriers of both CTAs,
+// and each CTA's epilogue warps drain their own 128 lanes of the accumulator.  No multicast load is used.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kPairStages = 6;
+constexpr int kPairWBytes = 2 * kWSpanBytes;            // this CTA's 128 columns of W: 16 KB
+constexpr int kPairStageBytes = kABytes + kPairWBytes;  // 32 KB
+
+struct PairStorage {
+    alignas(1024) uint8_t stage[kPairStages][kPairStageBytes];
+    alignas(8) uint64_t full[kPairStages];  // leader's copy is used: both CTAs' loads complete there
+    uint64_t empty[kPairStages];            // both CTAs (the leader's commits are multicast)
+    uint64_t acc_full[2];                   // both CTAs
+    uint64_t acc_empty[2];                  // leader's copy: 8 arrivals, the epilogue warps of both CTAs
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory object in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(const void* ptr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(ptr)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tiled load into this CTA's shared memory whose completion is counted on a barrier of either CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, int cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, int cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// Arrives once on `bar` in BOTH CTAs when every tcgen05 operation issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
+                     "r"(smem_u32(bar)),
+                 "h"(mask)
+                 : "memory");
+}
+// Instruction descriptor: fp32 accumulate, bf16 A and B, M = 256 over the pair, N = n.
+__host__ __device__ constexpr uint32_t instr_desc_pair(int a_mn_major, int b_mn_major, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | ((static_cast<uint32_t>(n) >> 3) << 17) | ((256u >> 4) << 24);
+}
+__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accum), "r"(0)
+        : "memory");
+}
+
+// Epilogue of one accumulator for one warp: thread = output row `grow` (TMEM lane of `t_addr`), columns
+// [col_base, col_base + 256) clipped to N.
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_addr, int grow, int col_base) {
+    const size_t row_off = static_cast<size_t>(grow) * p.N;
+#pragma unroll 1
+    for (int c = 0; c < kBN / 32; ++c) {
+        const int col0 = col_base + c * 32;
+        if (col0 >= p.N) break;  // the same for every thread of the CTA
+        uint32_t acc[32];
+        tmem_ld32(t_addr + c * 32, acc);
+        tmem_wait_ld();
+        if (grow < p.M) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int col = col0 + v * 8;
+                if (col >= p.N) break;
+                float z[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) z[i] = __uint_as_float(acc[v * 8 + i]);
+                if (p.bias != nullptr) {
+                    const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        z[2 * i] += __uint_as_float(bw[i] << 16);
+                        z[2 * i + 1] += __uint_as_float(bw[i] & 0xffff0000u);
+                    }
+                }
+                if (p.gelu) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) z[i] = z[i] / (1.0f + __expf(-1.702f * z[i]));
+                }
+                if (p.residual != nullptr) {
+                    const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + row_off + col);
+                    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        z[2 * i] += __uint_as_float(rw[i] << 16);
+                        z[2 * i + 1] += __uint_as_float(rw[i] & 0xffff0000u);
+                    }
+                }
+                uint4 w;
+                w.x = pack_bf16(z[0], z[1]);
+                w.y = pack_bf16(z[2], z[3]);
+                w.z = pack_bf16(z[4], z[5]);
+                w.w = pack_bf16(z[6], z[7]);
+                *reinterpret_cast<uint4*>(p.out + row_off + col) = w;
+            }
+        }
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    PairStorage& sm = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = static_cast<int>(cluster_ctarank());  // 0 = leader
+    const int cid = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const int n_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 rows x 256 columns
+    const int n_k = (p.K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sm.acc_full[a], 1);
+            mbar_init(&sm.acc_empty[a], 8);  // one arrival per epilogue warp of both CTAs
+        }
+        sm.abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(&sm.tmem_base, kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers are initialised before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both CTAs) ------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t it = 0;
+            for (int t = cid; t < n_tiles && ok; t += n_clusters) {
+                int tm, tn;
+                tile_coords(t, p, tm, tn);
+                for (int kb = 0; kb < n_k; ++kb, ++it) {
+                    const int s = it % kPairStages;
+                    ok = mbar_wait(&sm.empty[s], ((it / kPairStages) & 1) ^ 1);
+                    if (!ok) break;
+                    if (r == 0) mbar_arrive_expect_tx(&sm.full[s], 2 * kPairStageBytes);
+                    const uint32_t lead_full = map_to_cta(&sm.full[s], 0);
+                    tma_load_2d_pair(sm.stage[s], &tm_a, lead_full, kb * kBK, tm * 2 * kBM + r * kBM);
+#pragma unroll
+                    for (int sp = 0; sp < 2; ++sp)
+                        tma_load_2d_pair(sm.stage[s] + kABytes + sp * kWSpanBytes, &tm_w, lead_full,
+                                         tn * kBN + r * (kBN / 2) + sp * 64, kb * kBK);
+                }
+            }
+            if (!ok) sm.abort_flag = 1;
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+        if (lane == 0 && r == 0) {
+            constexpr uint32_t idesc = instr_desc_pair(0, 1, kBN);  // M = 256 over the pair, N = 256
+            bool ok = true;
+            uint32_t it = 0, local = 0;
+            for (int t = cid; t < n_tiles && ok; t += n_clusters, ++local) {
+                const uint32_t buf = local & 1;
+                ok = mbar_wait(&sm.acc_empty[buf], ((local >> 1) & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + buf * kBN;
+                for (int kb = 0; kb < n_k; ++kb, ++it) {
+                    const int s = it % kPairStages;
+                    ok = mbar_wait(&sm.full[s], (it / kPairStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = smem_desc(smem_u32(sm.stage[s]), 16, 1024);
+                    const uint64_t dw = smem_desc(smem_u32(sm.stage[s] + kABytes), kWSpanBytes, 1024);
+#pragma unroll
+                    for (int kk = 0; kk < kBK / 16; ++kk) {
+                        mma_ss_pair(d_tmem, da + static_cast<uint64_t>((kk * 32) >> 4),
+                                    dw + static_cast<uint64_t>((kk * 2048) >> 4), idesc, (kb | kk) ? 1u : 0u);
+                    }
+                    mma_commit_pair(&sm.empty[s]);
+                }
+                if (ok) mma_commit_pair(&sm.acc_full[buf]);
+            }
+            if (!ok) sm.abort_flag = 1;
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue (both CTAs): thread = output row ------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        bool ok = true;
+        uint32_t local = 0;
+        for (int t = cid; t < n_tiles && ok; t += n_clusters, ++local) {
+            int tm, tn;
+            tile_coords(t, p, tm, tn);
+            const uint32_t buf = local & 1;
+            ok = mbar_wait(&sm.acc_full[buf], (local >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            epilogue_rows(p, tmem + lane_base + buf * kBN, tm * 2 * kBM + r * kBM + row, tn * kBN);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(&sm.acc_empty[buf], 0));
+        }
+        if (!ok) sm.abort_flag = 1;
+    }
+
+    // common exit: every warp of both CTAs arrives here, then each CTA's allocating warp releases the pair's
+    // tensor memory
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, kTmemCols);
     }
 }
 
@@ -286,16 +495,57 @@ extern "C" int b2kv_matmul(const void* a, const void* w, const void* bias, const
                        static_cast<__nv_bfloat16*>(out), M, N, K, activation, static_cast<int>(tiles_m),
                        static_cast<int>(tiles_n)};
     constexpr size_t smem = sizeof(gemm::SharedStorage) + 1024;
+    constexpr size_t smem_pair = sizeof(gemm::PairStorage) + 1024;
     static bool configured[64] = {false};
     static int sm_count[64] = {0};
+    static int max_clusters[64] = {0};  // CTA pairs of gemm_pair_kernel that can be resident together
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
+    auto pair_config = [&](cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, unsigned grid) {
+        cfg = cudaLaunchConfig_t{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(gemm::kThreads);
+        cfg.dynamicSmemBytes = smem_pair;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    };
     if (!configured[dev]) {
         B2KV_CUDA_TRY(cudaFuncSetAttribute(gemm::gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem)));
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(gemm::gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem_pair)));
         B2KV_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        pair_config(cfg, attr, 2u * static_cast<unsigned>(sm_count[dev]));
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm::gemm_pair_kernel, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        max_clusters[dev] = n;
         configured[dev] = true;
+    }
+    // "gemm_variant": 0 = choose, 1 = one CTA per tile, 2 = CTA pairs.  The pair form needs (nearly) every SM
+    // to be reachable by a cluster of two; its 256-row tiles pay off from a few hundred rows on.
+    const int variant = tune_get("gemm_variant");
+    const bool pairs_fill = 2 * max_clusters[dev] >= sm_count[dev] - 8;
+    const bool use_pair = max_clusters[dev] > 0 && (variant == 2 || (variant == 0 && pairs_fill && M > 2 * gemm::kBM));
+    if (use_pair) {
+        p.tiles_m = static_cast<int>((static_cast<long long>(M) + 2 * gemm::kBM - 1) / (2 * gemm::kBM));
+        const long long clusters = std::min<long long>(static_cast<long long>(p.tiles_m) * p.tiles_n, max_clusters[dev]);
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        pair_config(cfg, attr, static_cast<unsigned>(2 * clusters));
+        B2KV_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm::gemm_pair_kernel, ta, tw, p));
+        B2KV_CUDA_TRY(cudaGetLastError());
+        return B2KV_OK;
     }
     const long long grid = std::min<long long>(tiles_m * tiles_n, sm_count[dev]);
     gemm::gemm_tc_kernel<<<static_cast<unsigned>(grid), gemm::kThreads, smem, static_cast<cudaStream_t>(stream)>>>(ta, tw, p);

@@ -168,9 +168,20 @@ def test_matmul_checks(pkg, ctx):
     (2048, 512, 4096, "bias"),     # more column tiles than a band has row tiles
     (3000, 256, 264, "gelu"),      # a last column tile of 8 columns
 ])
-def test_matmul_tiled_gemm_vs_oracle(pkg, ctx, M, K, N, epilogue):
-    """The tiled tensor-core GEMM behind ``matmul`` for more rows than a decode step has, with each
-    epilogue, against a float64 product."""
+@pytest.mark.parametrize("variant", [1, 2])
+def test_matmul_tiled_gemm_vs_oracle(pkg, ctx, M, K, N, epilogue, variant):
+    """The tiled tensor-core GEMM behind ``matmul`` for more rows than a decode step has, in both forms
+    (one CTA per 128 x 256 tile; a CTA pair per 256 x 256 tile), with each epilogue, against a float64
+    product."""
+    gpu = pkg.gpu
+    pkg._native.tune("gemm_variant", variant)
+    try:
+        _tiled_gemm_case(pkg, ctx, M, K, N, epilogue)
+    finally:
+        pkg._native.tune("gemm_variant", 0)
+
+
+def _tiled_gemm_case(pkg, ctx, M, K, N, epilogue):
     gpu = pkg.gpu
     A, W = _bf16(ctx, (M, K), 41), _bf16(ctx, (K, N), 42, scale=K ** -0.5)
     bias = _bf16(ctx, (N,), 43) if epilogue in ("all", "bias") else None
