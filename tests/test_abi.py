@@ -76,6 +76,13 @@ def test_argument_checks_return_before_any_launch(pkg):
     # prefill: K cache given without V cache
     assert lib.b2kv_prefill(A, A, A, A, None, None, A, None, 0, 0, 0, 8, 1, 8, 1, 64, 0, None) == -1
     assert lib.b2kv_prefill(A, A, A, A, None, None, None, None, 0, 0, 0, 0, 1, 0, 1, 64, 0, None) == -1
+    # matmul: fp32 is not taken, a missing operand, an inner dimension whose rows are not whole 16-byte chunks,
+    # a misaligned residual
+    assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 0, 0, None) == -3
+    assert lib.b2kv_matmul(A, None, None, None, A, 256, 128, 128, 0, 1, None) == -1
+    assert lib.b2kv_matmul(A, A, None, None, A, 256, 100, 128, 0, 1, None) == -3
+    assert lib.b2kv_matmul(A, A, None, A + 2, A, 256, 128, 128, 0, 1, None) == -2
+    assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 2, 1, None) == -1
 
 
 def test_workspace_size_grows_with_the_problem(pkg):
