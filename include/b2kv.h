@@ -87,6 +87,18 @@ int b2kv_append_paged(const void* new_k, const void* new_v, void* k_pool, void* 
                       int32_t* dev_status, void* stream);
 
 /*
+ * A whole prompt into a paged cache: rows [b * n_rows + i] of k_rows / v_rows ([B * n_rows, H * D], the layout
+ * flash_attention takes its K and V in, simple-llm/src/gpu/gpu_pass_forward.py:497-509) go to position
+ * first_pos + i of sequence b through the block table.  No counterpart in the reference (its cache is
+ * contiguous and filled one token per kv_cache_update call, gpu_kv_cache.py:113-186); it is what the fused
+ * cache write of b2kv_prefill does for a contiguous cache.  No length is advanced.
+ */
+int b2kv_append_rows_paged(const void* k_rows, const void* v_rows, void* k_pool, void* v_pool, const int32_t* block_table,
+                           int max_blocks, int block_size, int n_blocks, int B, int n_rows, int first_pos, int H, int D,
+                           int64_t stride_blk, int64_t stride_t, int64_t stride_h, int dtype, int32_t* dev_status,
+                           void* stream);
+
+/*
  * Cache gather: writes the logical view out[B, T_out, H, D] (contiguous) of the first
  * seq_lens[b] (or `len`) rows of every sequence, zero beyond.  The reference reads caches
  * back with gpu_buffer_2d_read (simple-llm/src/gpu/gpu_buffer.py:198-208), which only

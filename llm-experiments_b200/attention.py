@@ -4,15 +4,16 @@ Mirrors simple-llm/src/gpu/gpu_pass_forward.py:497-588: same positional argument
 checks and ``ValueError`` texts (:531-555), ``None`` returned, O / L / M written in place.
 ``flash_attn_bc`` / ``flash_attn_br`` are ignored (the CUDA kernels choose their own tiles).
 Extension: ``cache`` / ``layer_idx`` also write K and V rows 0..N-1 of every sequence into
-that cache layer in the same kernel and set the cache length to N, which the reference can
-only do token by token through ``kv_cache_update``.
+that cache layer (in the same kernel for a contiguous cache, through the block table by a copy
+kernel behind it for a paged one) and set the cache length to N, which the reference can only
+do token by token through ``kv_cache_update``.
 """
 from __future__ import annotations
 
 from typing import Optional
 
 from . import _native
-from .batch import batch_op_begin, validate_buffer_shape_1d, validate_buffer_shape_2d
+from .batch import batch_op_begin, dev_status_ptr, validate_buffer_shape_1d, validate_buffer_shape_2d
 from .kv_cache import cache_strides, dtype_code
 from .types import GPUBuffer1D, GPUBuffer2D, GPUContext, KVCache
 
@@ -52,8 +53,6 @@ def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffe
     if cache is not None:
         if layer_idx < 0 or layer_idx >= len(cache.layers):
             raise ValueError(f"layer_idx {layer_idx} out of range [0, {len(cache.layers)})")
-        if cache.block_table is not None:
-            raise ValueError("prefill into a paged cache is not supported; append token by token")
         if (cache.batch_size, cache.n_heads, cache.head_dim) != (batch_size, n_heads, head_dim):
             raise ValueError("cache dimensions do not match the attention call")
         if seq_len > cache.max_seq_len:
@@ -61,9 +60,10 @@ def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffe
         if cache.dtype != dtype:
             raise ValueError(f"cache dtype {cache.dtype} does not match {dtype}")
         layer = cache.layers[layer_idx]
-        kc, vc = layer.k_cache.buffer.data_ptr(), layer.v_cache.buffer.data_ptr()
         s0, st, sh = cache_strides(cache)
-        t_max = cache.max_seq_len
+        if cache.block_table is None:  # contiguous: the attention kernel writes the rows itself
+            kc, vc = layer.k_cache.buffer.data_ptr(), layer.v_cache.buffer.data_ptr()
+            t_max = cache.max_seq_len
 
     stream = batch_op_begin(ctx)
     rc = _native.lib.b2kv_prefill(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(), O.buffer.data_ptr(),
@@ -71,6 +71,14 @@ def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffe
                                   None if M is None else M.buffer.data_ptr(), kc, vc, s0, st, sh, t_max, batch_size,
                                   seq_len, n_heads, head_dim, dtype_code(dtype), stream)
     _native.check(rc)
+    if cache is not None and cache.block_table is not None:
+        # paged: the prompt's rows are scattered through the block table by a copy kernel behind the attention
+        rc = _native.lib.b2kv_append_rows_paged(K.buffer.data_ptr(), V.buffer.data_ptr(), layer.k_cache.buffer.data_ptr(),
+                                                layer.v_cache.buffer.data_ptr(), cache.block_table.data_ptr(),
+                                                cache.block_table.shape[1], cache.block_size, cache.n_blocks, batch_size,
+                                                seq_len, 0, n_heads, head_dim, s0, st, sh, dtype_code(dtype),
+                                                dev_status_ptr(ctx), stream)
+        _native.check(rc)
     if cache is not None:
         cache.current_len = seq_len
         if cache.seq_lens is not None:

@@ -122,3 +122,48 @@ def test_prefill_cta_pair_kernel_vs_oracle_and_one_cta_kernel(pkg, ctx, B, N, H,
         vview = U.logical_view(cache2, cache2.layers[0], "v")
         assert torch.equal(kview[:, :N].reshape(B, N, E), K) and torch.equal(vview[:, :N].reshape(B, N, E), V)
         assert float(kview[:, N:].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype,D,N", [(torch.bfloat16, 128, 200), (torch.float32, 64, 77), (torch.bfloat16, 128, 256)])
+def test_prefill_into_a_paged_cache_bit_exact_then_decode_continues(pkg, ctx, dtype, D, N):
+    """flash_attention with a paged cache: the prompt's K / V rows land in the blocks that a permuted block
+    table names (bit-exact, nothing else in the pool touched), and decoding the last prompt token over the
+    pool reproduces the prefill's last row."""
+    gpu = pkg.gpu
+    B, H, T_max, bs = 2, 3, 320, 16
+    E = H * D
+    Q = U.randn((B, N, E), dtype, ctx.device, 31)
+    K = U.randn((B, N, E), dtype, ctx.device, 32)
+    V = U.randn((B, N, E), dtype, ctx.device, 33)
+    n_blocks = 64
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=dtype, block_size=bs, n_blocks=n_blocks))
+    max_blocks = cache.block_table.shape[1]
+    g = torch.Generator().manual_seed(5)
+    perm = torch.randperm(n_blocks, generator=g)[: B * max_blocks].to(torch.int32)
+    cache.block_table.copy_(perm.reshape(B, max_blocks).to(ctx.device))
+    layer = cache.layers[0]
+    layer.k_cache.buffer.fill_(3.0)  # a sentinel in every block
+    layer.v_cache.buffer.fill_(3.0)
+    O, _, _ = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, cache=cache, stats=False)
+    assert cache.current_len == N
+    gpu.batch_begin(ctx)
+    kview = gpu.kv_cache_gather(ctx, cache, 0, "k", length=N)
+    vview = gpu.kv_cache_gather(ctx, cache, 0, "v", length=N)
+    gpu.batch_commit(ctx)
+    assert torch.equal(kview.reshape(B, N, E), K) and torch.equal(vview.reshape(B, N, E), V)
+    # rows written: B * N * E elements per pool; every other element still holds the sentinel
+    assert int((layer.k_cache.buffer != 3.0).sum()) <= B * N * E
+    used_blocks = (N + bs - 1) // bs
+    pool = layer.k_cache.buffer.reshape(n_blocks, -1)
+    untouched = torch.ones(n_blocks, dtype=torch.bool)
+    untouched[cache.block_table[:, :used_blocks].reshape(-1).cpu().long()] = False
+    assert bool((pool[untouched.to(ctx.device)] == 3.0).all())
+    q_last = Q[:, N - 1].contiguous()
+    out = torch.empty_like(q_last)
+    gpu.batch_begin(ctx)
+    gpu.attention_with_kv_cache(ctx, cache, 0, U.buf2d(pkg, ctx, q_last), U.buf2d(pkg, ctx, out))
+    gpu.batch_commit(ctx)
+    tol = U.TOL[dtype]
+    np.testing.assert_allclose(U.to_f32(out), U.to_f32(O.reshape(B, N, E)[:, N - 1]), rtol=max(tol["rtol"], 1e-4),
+                               atol=tol["atol"])
