@@ -291,7 +291,8 @@ int b2kv_matmul(const void* a, const void* w, const void* bias, const void* resi
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,
  * N a multiple of 256, "matmul_splits": ranges of input features per tile in b2kv_matmul_rows,
- * "gemm_variant": 1 = one CTA per output tile, 2 = CTA pairs in b2kv_matmul);
+ * "gemm_variant": 1 = one CTA per output tile, 2 / 3 = CTA pairs with 64 / 128 input features per
+ * ring stage in b2kv_matmul);
  * returns B2KV_ERR_BAD_ARG
  * for an unknown name.  Defaults are chosen per shape when a knob is 0.  No counterpart in
  * the reference beyond the tile-size fields of GPUConfig (gpu_types.py:69-121).

@@ -29,7 +29,7 @@ static Knob g_knobs[] = {
     {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
     {"prefill_variant", 0},
     {"matmul_splits", 0},  // ranges of input features per tile in b2kv_matmul_rows (0 = by shape)
-    {"gemm_variant", 0},   // b2kv_matmul: 0 = by shape and device, 1 = one CTA per tile, 2 = CTA pairs
+    {"gemm_variant", 0},   // b2kv_matmul: 0 = by shape and device, 1 = one CTA per tile, 2 / 3 = CTA pairs, 64 / 128 features per stage
 };
 
 int tune_get(const char* name) {

@@ -212,17 +212,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // the same again in TMA writes, which holds its tensor pipe at 80 %.  The copies of both CTAs complete on
 // the leader's barriers, one thread of the leader issues the MMAs and commits to the barriers of both CTAs,
 // and each CTA's epilogue warps drain their own 128 lanes of the accumulator.  No multicast load is used.
+// The ring holds 128 input features per stage in three stages by default (the issuing thread then waits,
+// fences and commits once per eight MMAs; 4 - 5 % faster than 64 features in six stages).
 // ---------------------------------------------------------------------------------------------------
-constexpr int kPairStages = 6;
-constexpr int kPairWBytes = 2 * kWSpanBytes;            // this CTA's 128 columns of W: 16 KB
-constexpr int kPairStageBytes = kABytes + kPairWBytes;  // 32 KB
-
+// kBKP input features per ring stage (64 or 128: one or two 128-byte swizzle spans of A), kStagesP stages.
+template <int kBKP, int kStagesP>
 struct PairStorage {
-    alignas(1024) uint8_t stage[kPairStages][kPairStageBytes];
-    alignas(8) uint64_t full[kPairStages];  // leader's copy is used: both CTAs' loads complete there
-    uint64_t empty[kPairStages];            // both CTAs (the leader's commits are multicast)
-    uint64_t acc_full[2];                   // both CTAs
-    uint64_t acc_empty[2];                  // leader's copy: 8 arrivals, the epilogue warps of both CTAs
+    static constexpr int kABytesP = kBM * kBKP * 2;       // this CTA's 128 rows of A
+    static constexpr int kWSpanP = kBKP * 128;            // kBKP input features x 64 columns
+    static constexpr int kStageBytesP = kABytesP + 2 * kWSpanP;  // + this CTA's 128 columns of W
+    alignas(1024) uint8_t stage[kStagesP][kStageBytesP];
+    alignas(8) uint64_t full[kStagesP];  // leader's copy is used: both CTAs' loads complete there
+    uint64_t empty[kStagesP];            // both CTAs (the leader's commits are multicast)
+    uint64_t acc_full[2];                // both CTAs
+    uint64_t acc_empty[2];               // leader's copy: 8 arrivals, the epilogue warps of both CTAs
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -338,18 +341,21 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ad
     }
 }
 
+template <int kBKP, int kStagesP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    PairStorage& sm = *reinterpret_cast<PairStorage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using Smem = PairStorage<kBKP, kStagesP>;
+    constexpr int kABytesP = Smem::kABytesP, kWSpanP = Smem::kWSpanP, kStageBytesP = Smem::kStageBytesP;
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = static_cast<int>(cluster_ctarank());  // 0 = leader
     const int cid = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
     const int n_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 rows x 256 columns
-    const int n_k = (p.K + kBK - 1) / kBK;
+    const int n_k = (p.K + kBKP - 1) / kBKP;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPairStages; ++s) {
+        for (int s = 0; s < kStagesP; ++s) {
             mbar_init(&sm.full[s], 1);
             mbar_init(&sm.empty[s], 1);
         }
@@ -379,16 +385,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 int tm, tn;
                 tile_coords(t, p, tm, tn);
                 for (int kb = 0; kb < n_k; ++kb, ++it) {
-                    const int s = it % kPairStages;
-                    ok = mbar_wait(&sm.empty[s], ((it / kPairStages) & 1) ^ 1);
+                    const int s = it % kStagesP;
+                    ok = mbar_wait(&sm.empty[s], ((it / kStagesP) & 1) ^ 1);
                     if (!ok) break;
-                    if (r == 0) mbar_arrive_expect_tx(&sm.full[s], 2 * kPairStageBytes);
+                    if (r == 0) mbar_arrive_expect_tx(&sm.full[s], 2 * kStageBytesP);
                     const uint32_t lead_full = map_to_cta(&sm.full[s], 0);
-                    tma_load_2d_pair(sm.stage[s], &tm_a, lead_full, kb * kBK, tm * 2 * kBM + r * kBM);
+#pragma unroll
+                    for (int ks = 0; ks < kBKP / 64; ++ks)  // 64 input features (one swizzle span) per box of A
+                        tma_load_2d_pair(sm.stage[s] + ks * (kBM * 128), &tm_a, lead_full, kb * kBKP + ks * 64,
+                                         tm * 2 * kBM + r * kBM);
 #pragma unroll
                     for (int sp = 0; sp < 2; ++sp)
-                        tma_load_2d_pair(sm.stage[s] + kABytes + sp * kWSpanBytes, &tm_w, lead_full,
-                                         tn * kBN + r * (kBN / 2) + sp * 64, kb * kBK);
+                        tma_load_2d_pair(sm.stage[s] + kABytesP + sp * kWSpanP, &tm_w, lead_full,
+                                         tn * kBN + r * (kBN / 2) + sp * 64, kb * kBKP);
                 }
             }
             if (!ok) sm.abort_flag = 1;
@@ -407,16 +416,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 tc_fence_after();
                 const uint32_t d_tmem = tmem + buf * kBN;
                 for (int kb = 0; kb < n_k; ++kb, ++it) {
-                    const int s = it % kPairStages;
-                    ok = mbar_wait(&sm.full[s], (it / kPairStages) & 1);
+                    const int s = it % kStagesP;
+                    ok = mbar_wait(&sm.full[s], (it / kStagesP) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t da = smem_desc(smem_u32(sm.stage[s]), 16, 1024);
-                    const uint64_t dw = smem_desc(smem_u32(sm.stage[s] + kABytes), kWSpanBytes, 1024);
+                    const uint64_t dw = smem_desc(smem_u32(sm.stage[s] + kABytesP), kWSpanP, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; ++kk) {
-                        mma_ss_pair(d_tmem, da + static_cast<uint64_t>((kk * 32) >> 4),
-                                    dw + static_cast<uint64_t>((kk * 2048) >> 4), idesc, (kb | kk) ? 1u : 0u);
+                    for (int kk = 0; kk < kBKP / 16; ++kk) {
+                        // A: 32 bytes inside a swizzle span, next span after four slices; W: 16 rows of 128 bytes
+                        const int a_off = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
+                        mma_ss_pair(d_tmem, da + static_cast<uint64_t>(a_off >> 4), dw + static_cast<uint64_t>((kk * 2048) >> 4),
+                                    idesc, (kb | kk) ? 1u : 0u);
                     }
                     mma_commit_pair(&sm.empty[s]);
                 }
@@ -495,18 +506,23 @@ extern "C" int b2kv_matmul(const void* a, const void* w, const void* bias, const
                        static_cast<__nv_bfloat16*>(out), M, N, K, activation, static_cast<int>(tiles_m),
                        static_cast<int>(tiles_n)};
     constexpr size_t smem = sizeof(gemm::SharedStorage) + 1024;
-    constexpr size_t smem_pair = sizeof(gemm::PairStorage) + 1024;
+    using Pair64 = gemm::PairStorage<64, 6>;
+    using Pair128 = gemm::PairStorage<128, 3>;
+    constexpr size_t smem_pair = sizeof(Pair64) + 1024;
+    constexpr size_t smem_pair128 = sizeof(Pair128) + 1024;
+    auto pair64 = gemm::gemm_pair_kernel<64, 6>;
+    auto pair128 = gemm::gemm_pair_kernel<128, 3>;
     static bool configured[64] = {false};
     static int sm_count[64] = {0};
     static int max_clusters[64] = {0};  // CTA pairs of gemm_pair_kernel that can be resident together
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
-    auto pair_config = [&](cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, unsigned grid) {
+    auto pair_config = [&](cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, unsigned grid, size_t bytes) {
         cfg = cudaLaunchConfig_t{};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(gemm::kThreads);
-        cfg.dynamicSmemBytes = smem_pair;
+        cfg.dynamicSmemBytes = bytes;
         cfg.stream = static_cast<cudaStream_t>(stream);
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
@@ -518,32 +534,42 @@ extern "C" int b2kv_matmul(const void* a, const void* w, const void* bias, const
     if (!configured[dev]) {
         B2KV_CUDA_TRY(cudaFuncSetAttribute(gemm::gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(smem)));
-        B2KV_CUDA_TRY(cudaFuncSetAttribute(gemm::gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           static_cast<int>(smem_pair)));
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(pair64, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_pair)));
+        B2KV_CUDA_TRY(cudaFuncSetAttribute(pair128, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_pair128)));
         B2KV_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
-        pair_config(cfg, attr, 2u * static_cast<unsigned>(sm_count[dev]));
+        pair_config(cfg, attr, 2u * static_cast<unsigned>(sm_count[dev]), smem_pair);
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm::gemm_pair_kernel, &cfg) != cudaSuccess) {
+        if (cudaOccupancyMaxActiveClusters(&n, pair64, &cfg) != cudaSuccess) {
             (void)cudaGetLastError();
             n = 0;
         }
         max_clusters[dev] = n;
         configured[dev] = true;
     }
-    // "gemm_variant": 0 = choose, 1 = one CTA per tile, 2 = CTA pairs.  The pair form needs (nearly) every SM
-    // to be reachable by a cluster of two; its 256-row tiles pay off from a few hundred rows on.
+    // "gemm_variant": 0 = choose (CTA pairs with 128 input features per stage where pairs fill the device),
+    // 1 = one CTA per tile, 2 = CTA pairs with 64 input features per stage and six stages, 3 = CTA pairs with 128
+    // and three stages.  The pair form needs (nearly) every SM to be reachable by a cluster of two; its 256-row
+    // tiles pay off from a few hundred rows on.
     const int variant = tune_get("gemm_variant");
     const bool pairs_fill = 2 * max_clusters[dev] >= sm_count[dev] - 8;
-    const bool use_pair = max_clusters[dev] > 0 && (variant == 2 || (variant == 0 && pairs_fill && M > 2 * gemm::kBM));
+    const bool use_pair =
+        max_clusters[dev] > 0 && (variant == 2 || variant == 3 || (variant == 0 && pairs_fill && M > 2 * gemm::kBM));
     if (use_pair) {
         p.tiles_m = static_cast<int>((static_cast<long long>(M) + 2 * gemm::kBM - 1) / (2 * gemm::kBM));
         const long long clusters = std::min<long long>(static_cast<long long>(p.tiles_m) * p.tiles_n, max_clusters[dev]);
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
-        pair_config(cfg, attr, static_cast<unsigned>(2 * clusters));
-        B2KV_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm::gemm_pair_kernel, ta, tw, p));
+        if (variant != 2) {  // default: 128 input features per stage (half as many barrier round trips per flop)
+            CUtensorMap tw128;
+            if (!gemm::make_map(&tw128, w, K, N, 128)) return B2KV_ERR_UNSUPPORTED;
+            pair_config(cfg, attr, static_cast<unsigned>(2 * clusters), smem_pair128);
+            B2KV_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair128, ta, tw128, p));
+        } else {
+            pair_config(cfg, attr, static_cast<unsigned>(2 * clusters), smem_pair);
+            B2KV_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair64, ta, tw, p));
+        }
         B2KV_CUDA_TRY(cudaGetLastError());
         return B2KV_OK;
     }

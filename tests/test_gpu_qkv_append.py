@@ -168,10 +168,11 @@ def test_matmul_checks(pkg, ctx):
     (2048, 512, 4096, "bias"),     # more column tiles than a band has row tiles
     (3000, 256, 264, "gelu"),      # a last column tile of 8 columns
 ])
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 def test_matmul_tiled_gemm_vs_oracle(pkg, ctx, M, K, N, epilogue, variant):
     """The tiled tensor-core GEMM behind ``matmul`` for more rows than a decode step has, in both forms
-    (one CTA per 128 x 256 tile; a CTA pair per 256 x 256 tile), with each epilogue, against a float64
+    (1: one CTA per 128 x 256 tile; 2, 3: a CTA pair per 256 x 256 tile with 64 or 128 input features per
+    ring stage), with each epilogue, against a float64
     product."""
     gpu = pkg.gpu
     pkg._native.tune("gemm_variant", variant)
