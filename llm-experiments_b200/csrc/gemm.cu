@@ -4,7 +4,8 @@
 // prompt-side projections either side of flash_attention (call sites src/wgpu_backend.py:812-930: Q / K / V,
 // the output projection, the MLP), with the bias_add, gelu and residual_add dispatches that follow a
 // matmul there folded into the epilogue.  Decode-step shapes (at most 128 rows) go to the weight-streaming
-// kernel in qkv_append.cu instead.
+// kernel in qkv_append.cu instead.  Two forms: one CTA per output tile (described first) and a CTA pair per
+// tile (further down; the default where clusters of two can occupy every SM).
 //
 //   * persistent grid, one CTA per SM; a CTA walks output tiles of 128 rows x 256 columns.  Tiles are
 //     ordered in blocks of 8 row tiles x 16 column tiles (about one wave of CTAs), so that the CTAs running
