@@ -17,6 +17,7 @@ struct PrefillParams {
     int64_t stride_b, stride_t, stride_h;
     int B, N, H;
     float q_prescale;
+    int group;  // tensor-core kernel: (sequence, head) pairs whose row blocks are launched next to each other; 0 = by size, < 0 = all
 };
 
 // SIMT kernel: every supported head_dim and storage type.

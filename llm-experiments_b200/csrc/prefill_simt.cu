@@ -236,7 +236,7 @@ extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O
         if (!stride_ok(stride_b, es) || !stride_ok(stride_t, es) || !stride_ok(stride_h, es)) return B2KV_ERR_ALIGN;
     }
     PrefillParams p{Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, B, N, H,
-                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D)))};
+                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), tune_get("prefill_group")};
     if (!tune_get("prefill_force_simt")) {
         // "prefill_variant": 0 = one-CTA tensor-core kernel (default), 2 = CTA-pair kernel where its
         // shape limits allow
