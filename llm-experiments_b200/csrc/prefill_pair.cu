@@ -32,6 +32,8 @@
 // fall through to the common exit, where both CTAs meet before the tensor memory is released.
 #include <math.h>
 
+#include <algorithm>
+
 #include "prefill.cuh"
 #include "tc_ptx.cuh"
 #include "tma_map.cuh"
@@ -270,9 +272,17 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int r = static_cast<int>(cluster_ctarank());  // 0 = leader
     const int pair_idx = blockIdx.x >> 1;
     const int n_pb = p.N / (2 * kRows);
-    // heaviest row blocks (most K/V steps) first
-    const int pb = n_pb - 1 - pair_idx / (p.H * p.B);
-    const int bh = pair_idx % (p.H * p.B);
+    // Launch order as in the one-CTA kernel: groups of `group` (sequence, head) pairs, inside a group the heaviest
+    // row blocks (most K/V steps) first, so that the clusters running together share the K/V of few pairs in L2.
+    const int n_bh = p.H * p.B;
+    const int group = (p.group > 0 && p.group < n_bh) ? p.group : n_bh;
+    const int per_group = group * n_pb;
+    const int gi = pair_idx / per_group;
+    const int first_bh = gi * group;
+    const int here = min(group, n_bh - first_bh);
+    const int within = pair_idx - gi * per_group;
+    const int pb = n_pb - 1 - within / here;
+    const int bh = first_bh + within % here;
     const int b = bh / p.H, h = bh % p.H;
     const int q0 = pb * 2 * kRows;   // first query row of the pair
     const int n = 2 * pb + 2;        // K/V steps 0 .. 2 pb + 1
@@ -564,7 +574,9 @@ static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E, in
 
 }  // namespace pair
 
-int prefill_tensor_core_pair(const PrefillParams& p, int D, int dtype, void* stream) {
+int prefill_tensor_core_pair(const PrefillParams& p_in, int D, int dtype, void* stream) {
+    PrefillParams p = p_in;
+    if (p.group == 0) p.group = static_cast<int>(std::max<long long>(1, (32LL << 20) / (4LL * p.N * pair::kD)));
     if (dtype != B2KV_DTYPE_BF16 || D != pair::kD) return B2KV_ERR_UNSUPPORTED;
     if (p.N < 2 * pair::kRows || p.N % (2 * pair::kRows) != 0) return B2KV_ERR_UNSUPPORTED;
     const int E = p.H * D;
