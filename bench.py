@@ -447,6 +447,13 @@ def run_b200(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of prefill_tc_kernel per sequence at H=32, D=128, N=4096, from an
+# ncu capture of the 2-sequence case (`--workload prefill_small`: 211.3 MB read + 156.5 MB written per launch;
+# the algorithmic figure per sequence is Q + K + V + O + two cache copies = 6 x 33.5 MB).  Every sequence brings
+# the same traffic, so a full launch is this figure times its sequences.
+PREFILL_DRAM_BYTES_PER_SEQUENCE = int((211.3e6 + 156.5e6) / 2)
+
+
 def measured_tensor_peak():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -564,7 +571,8 @@ def run_prefill(args, w, rank, world):
         "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": achieved, "peak": sustained,
                      "unit": "TFLOP/s", "frac": achieved / sustained, "frac_of_burst": achieved / burst,
                      "peak_kind": kind + " (sustained cuBLAS bf16; kernel timed in a loop)",
-                     "algorithmic_flops_per_launch": flops, "traffic": None},
+                     "algorithmic_flops_per_launch": flops,
+                     "traffic": B * PREFILL_DRAM_BYTES_PER_SEQUENCE if (H, D, N) == (32, 128, 4096) else None},
         "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
