@@ -190,10 +190,13 @@ int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* ou
  * performs no cudaMalloc / cudaFree and calls no allocating routine.
  *
  * Limits and rules:
- *   - Shapes whose partials do not fit (B * H * (ceil(CTAs / H) + 2) slots of (D + 2) * 4 bytes,
- *     CTAs = the persistent grid, two per SM for 256-byte rows) are refused with
- *     B2KV_ERR_STATIC_LIMIT before anything is launched; use b2kv_decode with your own
- *     workspace for those.  The benchmark shape (B=64, H=32, D=128, bf16) needs about 13 MB.
+ *   - Shapes whose partials do not fit are refused with B2KV_ERR_STATIC_LIMIT before anything is
+ *     launched; use b2kv_decode with your own workspace for those.  The partials take
+ *     B * H * (ceil(CTAs / H) + 2) slots of (D + 2) * 4 bytes, where CTAs is the persistent grid:
+ *     the SM count times the resident CTAs per SM of the compiled variant (three for 256-byte
+ *     rows, at most four for any row size), and never more than the tiles of work.  The
+ *     benchmark shape (B=64, H=32, D=128, bf16; 444 CTAs on a 148-SM B200) needs 32768 slots
+ *     = 17.0 MB and fits; B=128 with the same heads does not.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call before starting
  *     any stream capture on that device.
@@ -203,7 +206,7 @@ int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* ou
  *     them) race on it: keep calls on one device in stream order.
  *   - Contiguous caches only (no block table).  Results are bit-identical to b2kv_decode.
  */
-#define B2KV_STATIC_SCRATCH_BYTES (16u << 20)
+#define B2KV_STATIC_SCRATCH_BYTES (32u << 20)
 int b2kv_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens,
                        int len, int len_bias, int B, int H, int D, int T_upper, int64_t stride_b, int64_t stride_t,
                        int64_t stride_h, int dtype, int32_t* dev_status, void* stream);

@@ -20,7 +20,7 @@ ERR_UNSUPPORTED = -3
 ERR_WORKSPACE = -4
 ERR_CUDA = -5
 ERR_STATIC_LIMIT = -6
-STATIC_SCRATCH_BYTES = 16 << 20
+STATIC_SCRATCH_BYTES = 32 << 20
 
 DEV_STATUS_TEXT = {
     1: "a block-table entry points outside the pool",

@@ -751,14 +751,13 @@ static int dispatch_dim(const DecodeParams& p, int D, void* out, void* ws, size_
     }
 }
 
-static int decode_entry(const void* q, const void* k, const void* v, void* out, const int32_t* seq_lens, int len,
-                        int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
-                        int H, int D, int T_upper, int64_t s0, int64_t st, int64_t sh, int dtype, void* workspace,
-                        size_t workspace_bytes, int32_t* dev_status, void* stream, const GatherInfo* gather = nullptr,
-                        float* partial_out = nullptr) {
+// Argument checks shared by every decode entry point; nothing touches the device here.
+static int decode_check_args(const void* q, const void* k, const void* v, const void* out, bool out_optional,
+                             const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B, int H,
+                             int D, int T_upper, int64_t s0, int64_t st, int64_t sh, int dtype, const void* workspace) {
     const int es = elt_bytes(dtype);
     if (es == 0) return B2KV_ERR_UNSUPPORTED;
-    if (!q || !k || !v || (!out && !gather)) return B2KV_ERR_BAD_ARG;
+    if (!q || !k || !v || (!out && !out_optional)) return B2KV_ERR_BAD_ARG;
     if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0) return B2KV_ERR_BAD_ARG;
     if (static_cast<long long>(B) * H > 0x7fffffffLL / 4) return B2KV_ERR_UNSUPPORTED;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(workspace))
@@ -768,6 +767,17 @@ static int decode_entry(const void* q, const void* k, const void* v, void* out, 
     if (block_table && (max_blocks <= 0 || block_size <= 0 || n_blocks <= 0 ||
                         static_cast<long long>(max_blocks) * block_size < T_upper))
         return B2KV_ERR_BAD_ARG;
+    return B2KV_OK;
+}
+
+static int decode_entry(const void* q, const void* k, const void* v, void* out, const int32_t* seq_lens, int len,
+                        int len_bias, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
+                        int H, int D, int T_upper, int64_t s0, int64_t st, int64_t sh, int dtype, void* workspace,
+                        size_t workspace_bytes, int32_t* dev_status, void* stream, const GatherInfo* gather = nullptr,
+                        float* partial_out = nullptr) {
+    const int rc = decode_check_args(q, k, v, out, gather != nullptr, block_table, max_blocks, block_size, n_blocks, B, H,
+                                     D, T_upper, s0, st, sh, dtype, workspace);
+    if (rc != B2KV_OK) return rc;
     DecodeParams p{};
     p.q = q;
     p.k = k;
@@ -923,8 +933,13 @@ extern "C" int b2kv_decode_static(const void* q, const void* k_cache, const void
                                   const int32_t* seq_lens, int len, int len_bias, int B, int H, int D, int T_upper,
                                   int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype,
                                   int32_t* dev_status, void* stream) {
+    // argument checks first, so that a bad call is refused without touching the device
+    int rc = decode_check_args(q, k_cache, v_cache, out, false, nullptr, 0, 0, 0, B, H, D, T_upper, stride_b, stride_t,
+                               stride_h, dtype, nullptr);
+    if (rc != B2KV_OK) return rc;
+    if (D != 16 && D != 32 && D != 64 && D != 128 && D != 256) return B2KV_ERR_UNSUPPORTED;
     void* scratch = nullptr;
-    int rc = decode_static_scratch(&scratch);
+    rc = decode_static_scratch(&scratch);
     if (rc != B2KV_OK) return rc;
     // The partials need no clearing: every slot that the merge kernel reads is written by the
     // split kernel of the same call first.

@@ -70,6 +70,11 @@ def test_argument_checks_return_before_any_launch(pkg):
     # decode: head_dim that is not compiled, missing workspace handled after the shape checks
     assert lib.b2kv_decode(A, A, A, A, None, 4, 0, 1, 1, 48, 8, 384, 48, 48, 0, A, 1 << 20, None, None) == -3
     assert lib.b2kv_decode(A, A, A, A, None, 4, 0, 0, 1, 64, 8, 512, 64, 64, 0, A, 1 << 20, None, None) == -1
+    # decode without a workspace argument: the same checks come before the look-up of the built-in array
+    assert lib.b2kv_decode_static(None, A, A, A, None, 4, 0, 1, 1, 64, 8, 512, 64, 64, 0, None, None) == -1
+    assert lib.b2kv_decode_static(A, A, A, A, None, 4, 0, 1, 1, 64, 8, 512, 64, 64, 7, None, None) == -3
+    assert lib.b2kv_decode_static(A, A, A, A, None, 4, 0, 1, 1, 48, 8, 384, 48, 48, 0, None, None) == -3
+    assert lib.b2kv_decode_static(A, A + 8, A, A, None, 4, 0, 1, 1, 64, 8, 512, 64, 64, 0, None, None) == -2
     # paged decode: table smaller than the upper bound of the lengths
     assert lib.b2kv_decode_paged(A, A, A, A, None, 4, 0, A, 1, 16, 8, 1, 1, 64, 64, 1024, 64, 1024, 0, A, 1 << 20,
                                  None, None) == -1
