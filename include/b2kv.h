@@ -57,7 +57,7 @@ extern "C" {
 
 #define B2KV_DEV_BAD_BLOCK 1    /* block-table entry outside the pool           */
 #define B2KV_DEV_BAD_POSITION 2 /* append position outside [0, T_max)           */
-#define B2KV_DEV_WAIT_TIMEOUT 3 /* a bounded wait on a copy barrier ran out     */
+#define B2KV_DEV_WAIT_TIMEOUT 3 /* a bounded wait on a barrier ran out          */
 
 /* Text for a return code.  Replaces the reference's exception messages at the C level. */
 const char* b2kv_strerror(int status);
@@ -221,10 +221,12 @@ int b2kv_decode_static(const void* q, const void* k_cache, const void* v_cache, 
  * every sequence into the caches (same dtype, layout given by the cache strides), which
  * the reference can only do one token at a time through kv_cache_update.
  * bf16 with D == 128 or 64 runs on the tcgen05 tensor cores; other shapes run on a SIMT kernel.
+ * A tensor-core kernel whose bounded barrier wait ran out stores B2KV_DEV_WAIT_TIMEOUT in dev_status
+ * (the output of that launch is then incomplete).
  */
 int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache,
                  void* v_cache, int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B, int N, int H,
-                 int D, int dtype, void* stream);
+                 int D, int dtype, int32_t* dev_status, void* stream);
 
 /*
  * The tail of a cached generation step, fp32 like the reference's buffers.  Each replaces one
@@ -284,16 +286,20 @@ int b2kv_matmul_rows(const void* x, const void* w, const void* bias, const void*
  * the prompt-side projections either side of flash_attention (src/wgpu_backend.py:812-930), with the bias_add
  * (:211-248), gelu (:179-209) and residual_add (:250-283) dispatches that follow it there.  A persistent
  * tensor-core kernel over 128 x 256 output tiles; for at most 128 rows b2kv_matmul_rows streams the weights
- * faster.
+ * faster.  A bounded barrier wait that ran out stores B2KV_DEV_WAIT_TIMEOUT in dev_status (the output of that
+ * launch is then incomplete).
  */
 int b2kv_matmul(const void* a, const void* w, const void* bias, const void* residual, void* out, int M, int K, int N,
-                int activation, int dtype, void* stream);
+                int activation, int dtype, int32_t* dev_status, void* stream);
 
 /*
- * Tuning hook for experiments: sets an integer knob by name ("decode_variant",
+ * Tuning hook for experiments (process-global and unsynchronised: set knobs before launching work, never while
+ * another thread is inside a b2kv call): sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,
- * N a multiple of 256, "matmul_splits": ranges of input features per tile in b2kv_matmul_rows,
+ * N a multiple of 256, "prefill_test_expire": 1 = test hook, the softmax warps of the one-CTA tensor-core prefill
+ * behave as if their first bounded wait had run out (the launch then ends after about two seconds with
+ * B2KV_DEV_WAIT_TIMEOUT in dev_status), "matmul_splits": ranges of input features per tile in b2kv_matmul_rows,
  * "gemm_variant": 1 = one CTA per output tile, 2 / 3 = CTA pairs with 64 / 128 input features per
  * ring stage in b2kv_matmul);
  * returns B2KV_ERR_BAD_ARG

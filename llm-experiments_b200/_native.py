@@ -25,7 +25,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 DEV_STATUS_TEXT = {
     1: "a block-table entry points outside the pool",
     2: "an append position lies outside the cache",
-    3: "a bounded wait on a copy barrier ran out",
+    3: "a bounded wait on a barrier ran out",
 }
 
 _vp = ctypes.c_void_p
@@ -54,7 +54,7 @@ SIGNATURES = {
                                  _vp]),
     "b2kv_merge_partials": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "b2kv_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
-    "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp]),
+    "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "b2kv_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),
     "b2kv_layernorm_bf16": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),
     "b2kv_extract_last_tokens": (_i, [_vp, _vp, _i, _i, _i, _vp]),
@@ -62,7 +62,7 @@ SIGNATURES = {
     "b2kv_argmax": (_i, [_vp, _vp, _i, _i, _vp]),
     "b2kv_qkv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_matmul_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "b2kv_matmul": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b2kv_matmul": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "b2kv_tune": (_i, [ctypes.c_char_p, _i]),
 }
 

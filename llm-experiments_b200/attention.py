@@ -13,11 +13,12 @@ from __future__ import annotations
 from typing import Optional
 
 from . import _native
-from .batch import batch_op_begin, dev_status_ptr, validate_buffer_shape_1d, validate_buffer_shape_2d
+from .batch import batch_op_begin, dev_status_ptr, reference_op, validate_buffer_shape_1d, validate_buffer_shape_2d
 from .kv_cache import cache_strides, dtype_code
 from .types import GPUBuffer1D, GPUBuffer2D, GPUContext, KVCache
 
 
+@reference_op("flash_attention")
 def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffer2D, O: GPUBuffer2D,
                     L: Optional[GPUBuffer1D], M: Optional[GPUBuffer1D], batch_size: int, seq_len: int, n_heads: int,
                     head_dim: int, cache: Optional[KVCache] = None, layer_idx: int = 0) -> None:
@@ -69,7 +70,7 @@ def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffe
     rc = _native.lib.b2kv_prefill(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(), O.buffer.data_ptr(),
                                   None if L is None else L.buffer.data_ptr(),
                                   None if M is None else M.buffer.data_ptr(), kc, vc, s0, st, sh, t_max, batch_size,
-                                  seq_len, n_heads, head_dim, dtype_code(dtype), stream)
+                                  seq_len, n_heads, head_dim, dtype_code(dtype), dev_status_ptr(ctx), stream)
     _native.check(rc)
     if cache is not None and cache.block_table is not None:
         # paged: the prompt's rows are scattered through the block table by a copy kernel behind the attention

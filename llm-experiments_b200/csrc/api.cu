@@ -28,6 +28,7 @@ static Knob g_knobs[] = {
     {"decode_l2_keep", 0},  // 1 = K/V bulk copies use the default L2 policy instead of evict-first
     {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
     {"prefill_variant", 0},
+    {"prefill_test_expire", 0},  // test hook: 1 = the softmax warps of the one-CTA tensor-core prefill give up at once
     {"prefill_group", 0},  // one-CTA tensor-core prefill: (sequence, head) pairs per launch group; 0 = by size, -1 = all
     {"matmul_splits", 0},  // ranges of input features per tile in b2kv_matmul_rows (0 = by shape)
     {"gemm_variant", 0},   // b2kv_matmul: 0 = by shape and device, 1 = one CTA per tile, 2 / 3 = CTA pairs, 64 / 128 features per stage
@@ -72,7 +73,7 @@ const char* b2kv_strerror(int status) {
 
 const char* b2kv_last_cuda_error(void) { return b2kv::g_last_error; }
 
-int b2kv_version(void) { return 1; }
+int b2kv_version(void) { return 2; }
 
 int b2kv_tune(const char* name, int value) {
     if (name == nullptr) return B2KV_ERR_BAD_ARG;

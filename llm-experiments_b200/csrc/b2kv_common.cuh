@@ -112,15 +112,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: gives up after kWaitLimit polls (each poll itself blocks for a short,
-// hardware-defined time) and returns false, so that no kernel can spin for ever on a
-// barrier that will not complete.
+// Bounded wait: gives up after kWaitLimit polls or about kWaitLimitNs of wall time, whichever comes
+// first (a poll blocks for a short, hardware-defined time, so the polls alone do not say how long a
+// wait may last), and returns false, so that no kernel can spin for ever on a barrier that will not
+// complete.
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    for (uint32_t it = 0; it < 128; ++it)
         if (mbar_try_wait(bar, parity)) return true;
-        if (it > 128) __nanosleep(32);
+    const unsigned long long t0 = globaltimer_ns();
+    for (uint32_t it = 128; it < kWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(32);
+        if ((it & 255u) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) return false;
     }
     return false;
 }

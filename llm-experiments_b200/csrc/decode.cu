@@ -96,7 +96,7 @@ struct DecodeCfg {
     static constexpr int kAcc = kChunksPerLane * kEpc;
     static constexpr int kMergeFloats = NCW * (D + 2);
     static constexpr int kThreads = (NCW + 1) * 32;
-    static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + 2 * STAGES * sizeof(uint64_t) +
+    static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + (2 * STAGES + 2) * sizeof(uint64_t) +
                                          STAGES * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 128;
     static_assert(kRowBytes % 16 == 0, "rows must be whole 16-byte chunks");
     static_assert(kChunksPerRow >= 2, "a row must span at least two lanes");
@@ -311,8 +311,8 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES, int NCW>
 __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
-                                                uint64_t* empty, const StageMeta* meta, float* merge, int warp,
-                                                int lane) {
+                                                uint64_t* empty, uint64_t* merge_bar, const StageMeta* meta,
+                                                float* merge, int warp, int lane) {
     constexpr int LPR = Cfg::kLanesPerRow;
     constexpr int CPL = Cfg::kChunksPerLane;
     constexpr int EPC = Cfg::kEpc;
@@ -334,6 +334,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
     int stage = 0;
     uint32_t phase = 0;
     int parity = 0;  // which merge buffer the next finished item uses
+    uint32_t merge_phase = 0;  // phase of merge_bar that the next finished item completes
 
     while (true) {
         if (!mbar_wait(&full[stage], phase)) {
@@ -457,7 +458,16 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                     mb[D + 1] = l;
                 }
             }
-            named_barrier_sync<NCW * 32>(1);
+            // The warps meet on an mbarrier, not on a hardware named barrier, so that this wait is bounded
+            // like every other: should a sibling warp have given up on a copy barrier, the others run
+            // out here, report it and leave, instead of waiting for an arrival that never comes.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(merge_bar);
+            if (!mbar_wait(merge_bar, merge_phase)) {
+                report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+                return;
+            }
+            merge_phase ^= 1u;
             // all consumer threads: one output column each
             const float* mr = merge + parity * Cfg::kMergeFloats;
             float m_all = -INFINITY;
@@ -496,7 +506,8 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * Cfg::kStageBytes);
     uint64_t* empty = full + STAGES;
-    StageMeta* meta = reinterpret_cast<StageMeta*>(empty + STAGES);
+    uint64_t* merge_bar = empty + STAGES;  // the consumer warps meet here once per finished item
+    StageMeta* meta = reinterpret_cast<StageMeta*>(empty + STAGES + 2);
     float* merge = reinterpret_cast<float*>(meta + STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -505,13 +516,14 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NCW);
         }
+        mbar_init(merge_bar, NCW);
         fence_mbar_init();
     }
     __syncthreads();
     if (warp == NCW) {
         decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, lane);
     } else {
-        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, meta, merge, warp, lane);
+        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, merge_bar, meta, merge, warp, lane);
     }
 }
 

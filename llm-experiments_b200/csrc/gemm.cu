@@ -52,6 +52,7 @@ struct GemmParams {
     int M, N, K;
     int gelu;
     int tiles_m, tiles_n;
+    int32_t* dev_status;  // optional status word: receives B2KV_DEV_WAIT_TIMEOUT when a bounded wait ran out
 };
 
 struct SharedStorage {
@@ -203,6 +204,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+    if (threadIdx.x == 0 && sm.abort_flag) report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -468,6 +470,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         tc_fence_after();
         tmem_dealloc_pair(tmem, kTmemCols);
     }
+    if (threadIdx.x == 0 && sm.abort_flag) report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
 }
 
 // [rows, cols] bf16 row-major matrix, boxes of box_rows x 64 columns, 128-byte swizzle; reads outside the
@@ -491,7 +494,7 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int
 using namespace b2kv;
 
 extern "C" int b2kv_matmul(const void* a, const void* w, const void* bias, const void* residual, void* out, int M, int K,
-                           int N, int activation, int dtype, void* stream) {
+                           int N, int activation, int dtype, int32_t* dev_status, void* stream) {
     if (dtype != B2KV_DTYPE_BF16) return B2KV_ERR_UNSUPPORTED;
     if (!a || !w || !out) return B2KV_ERR_BAD_ARG;
     if (M <= 0 || K <= 0 || N <= 0 || activation < 0 || activation > 1) return B2KV_ERR_BAD_ARG;
@@ -505,7 +508,7 @@ extern "C" int b2kv_matmul(const void* a, const void* w, const void* bias, const
     if (!gemm::make_map(&ta, a, M, K, gemm::kBM) || !gemm::make_map(&tw, w, K, N, gemm::kBK)) return B2KV_ERR_UNSUPPORTED;
     gemm::GemmParams p{static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual),
                        static_cast<__nv_bfloat16*>(out), M, N, K, activation, static_cast<int>(tiles_m),
-                       static_cast<int>(tiles_n)};
+                       static_cast<int>(tiles_n), dev_status};
     constexpr size_t smem = sizeof(gemm::SharedStorage) + 1024;
     using Pair64 = gemm::PairStorage<64, 6>;
     using Pair128 = gemm::PairStorage<128, 3>;

@@ -17,6 +17,8 @@ struct PrefillParams {
     int64_t stride_b, stride_t, stride_h;
     int B, N, H;
     float q_prescale;
+    int32_t* dev_status;  // optional status word: receives B2KV_DEV_WAIT_TIMEOUT when a bounded wait ran out
+    int test_expire;      // test hook: the softmax warps of the one-CTA tensor-core kernel give up before their first wait
     int group;  // tensor-core kernel: (sequence, head) pairs whose row blocks are launched next to each other; 0 = by size, < 0 = all
 };
 

@@ -557,6 +557,7 @@ prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tc_fence_after();
         tmem_dealloc_pair(tmem, kPairTmemCols);
     }
+    if (threadIdx.x == 0 && sm.abort_flag) report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
 }
 
 // View of a [B*N, H*D] bf16 matrix as (x = column, y = row inside the sequence, z = sequence).

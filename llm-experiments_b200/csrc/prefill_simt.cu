@@ -222,7 +222,7 @@ using namespace b2kv;
 
 extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache,
                             void* v_cache, int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B,
-                            int N, int H, int D, int dtype, void* stream) {
+                            int N, int H, int D, int dtype, int32_t* dev_status, void* stream) {
     const int es = elt_bytes(dtype);
     if (es == 0) return B2KV_ERR_UNSUPPORTED;
     if (!Q || !K || !V || !O) return B2KV_ERR_BAD_ARG;
@@ -236,7 +236,8 @@ extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O
         if (!stride_ok(stride_b, es) || !stride_ok(stride_t, es) || !stride_ok(stride_h, es)) return B2KV_ERR_ALIGN;
     }
     PrefillParams p{Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, B, N, H,
-                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), tune_get("prefill_group")};
+                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), dev_status,
+                    tune_get("prefill_test_expire"), tune_get("prefill_group")};
     if (!tune_get("prefill_force_simt")) {
         // "prefill_variant": 0 = one-CTA tensor-core kernel (default), 2 = CTA-pair kernel where its
         // shape limits allow

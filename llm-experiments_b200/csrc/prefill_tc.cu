@@ -262,7 +262,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t o_tmem = tmem + lane_base + kColO + x * 128;
         const float c = p.q_prescale;  // log2(e) / sqrt(D)
         float m_used = -INFINITY, m_run = -INFINITY, l = 0.f;
-        bool ok = true;
+        bool ok = p.test_expire == 0;  // test hook: behave as if the first wait had run out
         for (int j = 0; j < n_x && ok; ++j) {
             ok = mbar_wait(&sm.s_full[x], j & 1);
             if (!ok) break;
@@ -374,13 +374,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     }
 
-    // common exit: every warp arrives here, then the allocating warp releases the tensor memory
+    // common exit: every warp arrives here, then the allocating warp releases the tensor memory and a
+    // wait that ran out anywhere in the CTA is reported to the host's status word
     tc_fence_before();
     __syncthreads();
     if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+    if (threadIdx.x == 0 && sm.abort_flag) report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
 }
 
 // View of a [B*N, H*D] bf16 matrix as (x = column, y = row inside the sequence, z = sequence), so

@@ -2,7 +2,15 @@
 KV-cache attention path and the tail of a generation step: callers write ``from <package> import gpu`` and use
 ``gpu.kv_cache_update(ctx, ...)`` exactly as with the reference's ``gpu`` module."""
 from .attention import flash_attention
-from .batch import batch_begin, batch_commit
+from .batch import (
+    batch_begin,
+    batch_commit,
+    perf_monitor_create,
+    perf_monitor_kernel_time_record,
+    perf_monitor_reset,
+    perf_monitor_stats_get,
+    perf_monitor_submission_record,
+)
 from .buffers import (
     gpu_buffer_1d_create,
     gpu_buffer_1d_read,
@@ -32,6 +40,8 @@ __all__ = [
     "gpu_buffer_1d_read", "gpu_buffer_2d_read", "gpu_buffer_zerofy",
     "flash_attention",
     "batch_begin", "batch_commit",
+    "perf_monitor_create", "perf_monitor_kernel_time_record", "perf_monitor_reset", "perf_monitor_stats_get",
+    "perf_monitor_submission_record",
     "kv_cache_create", "kv_cache_reset", "kv_cache_update", "attention_with_kv_cache",
     "kv_cache_gather", "kv_cache_set_lengths",
     "layernorm", "extract_last_tokens", "softmax", "argmax",

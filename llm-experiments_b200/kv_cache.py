@@ -23,7 +23,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from . import _native
-from .batch import batch_op_begin, dev_status_ptr, validate_buffer_shape_2d
+from .batch import batch_op_begin, dev_status_ptr, validate_buffer_shape_2d, reference_op
 from .buffers import gpu_buffer_2d_create, gpu_buffer_zerofy
 from .types import GPUBuffer2D, GPUContext, KVCache, KVCacheConfig, KVCacheLayer
 
@@ -116,6 +116,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+@reference_op("kv_cache_update")
 def kv_cache_update(ctx: GPUContext, cache: KVCache, layer_idx: int, new_k: GPUBuffer2D, new_v: GPUBuffer2D,
                     advance: bool = True) -> None:
     if layer_idx < 0 or layer_idx >= len(cache.layers):
@@ -161,6 +162,7 @@ def decode_workspace(cache: KVCache) -> torch.Tensor:
     return cache.workspace
 
 
+@reference_op("attention_with_kv_cache")
 def attention_with_kv_cache(ctx: GPUContext, cache: KVCache, layer_idx: int, q_new: GPUBuffer2D,
                             output: GPUBuffer2D) -> None:
     if layer_idx < 0 or layer_idx >= len(cache.layers):

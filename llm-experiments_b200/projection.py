@@ -13,11 +13,12 @@ from __future__ import annotations
 import torch
 
 from . import _native
-from .batch import batch_op_begin, dev_status_ptr, validate_buffer_shape_2d
+from .batch import batch_op_begin, dev_status_ptr, reference_op, validate_buffer_shape_2d
 from .kv_cache import _ptr, cache_strides, dtype_code
 from .types import GPUBuffer2D, GPUContext, KVCache
 
 
+@reference_op("matmul")
 def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, residual: GPUBuffer2D = None,
            bias=None, activation: str = None) -> None:
     """``C = A @ B`` with the reference's argument order and shape check
@@ -51,14 +52,18 @@ def matmul(ctx: GPUContext, A: GPUBuffer2D, B: GPUBuffer2D, C: GPUBuffer2D, resi
         raise ValueError("matmul needs inner and outer dimensions that are multiples of 8 (16-byte rows)")
     # the rows of a decode step stream the weights once (b2kv_matmul_rows); everything else is a tiled GEMM
     rows_kernel = M <= 128 and K % 128 == 0 and N % 128 == 0
-    fn = _native.lib.b2kv_matmul_rows if rows_kernel else _native.lib.b2kv_matmul
     stream = batch_op_begin(ctx)
-    rc = fn(A.buffer.data_ptr(), B.buffer.data_ptr(), None if bias is None else bias.buffer.data_ptr(),
+    args = (A.buffer.data_ptr(), B.buffer.data_ptr(), None if bias is None else bias.buffer.data_ptr(),
             None if residual is None else residual.buffer.data_ptr(), C.buffer.data_ptr(), M, K, N,
-            1 if activation == "gelu" else 0, dtype_code(torch.bfloat16), stream)
+            1 if activation == "gelu" else 0, dtype_code(torch.bfloat16))
+    if rows_kernel:
+        rc = _native.lib.b2kv_matmul_rows(*args, stream)
+    else:
+        rc = _native.lib.b2kv_matmul(*args, dev_status_ptr(ctx), stream)
     _native.check(rc)
 
 
+@reference_op("qkv_project_append")
 def qkv_project_append(ctx: GPUContext, cache: KVCache, layer_idx: int, x: GPUBuffer2D, wq: GPUBuffer2D,
                        wk: GPUBuffer2D, wv: GPUBuffer2D, q_out: GPUBuffer2D, advance: bool = True) -> None:
     """``q_out = x @ wq``; row ``current_len`` (or ``seq_lens[b]``) of the layer's K / V cache

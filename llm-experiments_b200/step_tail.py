@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import _native
-from .batch import batch_op_begin, validate_buffer_shape_1d, validate_buffer_shape_2d
+from .batch import batch_op_begin, reference_op, validate_buffer_shape_1d, validate_buffer_shape_2d
 from .types import GPUBuffer1D, GPUBuffer2D, GPUContext
 
 
@@ -24,6 +24,7 @@ def _f32(buf, name: str) -> int:
     return buf.buffer.data_ptr()
 
 
+@reference_op("layernorm")
 def layernorm(ctx: GPUContext, input_buf: GPUBuffer2D, gamma: GPUBuffer1D, beta: GPUBuffer1D,
               output: GPUBuffer2D) -> None:
     n_elements, size = input_buf.shape
@@ -45,6 +46,7 @@ def layernorm(ctx: GPUContext, input_buf: GPUBuffer2D, gamma: GPUBuffer1D, beta:
     _native.check(fn(*ptrs, n_elements, size, float(ctx.config.layernorm_epsilon), stream))
 
 
+@reference_op("extract_last_tokens")
 def extract_last_tokens(ctx: GPUContext, input_buf: GPUBuffer2D, output: GPUBuffer2D, batch_size: int, seq_len: int,
                         embedding_dim: int) -> None:
     if batch_size <= 0 or seq_len <= 0 or embedding_dim <= 0:
@@ -60,6 +62,7 @@ def extract_last_tokens(ctx: GPUContext, input_buf: GPUBuffer2D, output: GPUBuff
     _native.check(_native.lib.b2kv_extract_last_tokens(src, dst, batch_size, seq_len, embedding_dim, stream))
 
 
+@reference_op("softmax")
 def softmax(ctx: GPUContext, logits: GPUBuffer2D, probs: GPUBuffer2D) -> None:
     if logits.shape != probs.shape:
         raise ValueError(f"Softmax shape mismatch: logits {logits.shape} != probs {probs.shape}")
@@ -69,6 +72,7 @@ def softmax(ctx: GPUContext, logits: GPUBuffer2D, probs: GPUBuffer2D) -> None:
     _native.check(_native.lib.b2kv_softmax(src, dst, batch_size, vocab_size, stream))
 
 
+@reference_op("argmax")
 def argmax(ctx: GPUContext, values: GPUBuffer2D, indices: GPUBuffer1D) -> None:
     """``indices[b]`` = index of the largest value of row b (int32; the lowest index among equals)."""
     batch_size, vocab_size = values.shape

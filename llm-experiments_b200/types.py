@@ -10,7 +10,7 @@ its behaviour (fp32, one shared ``current_len``, ``[B*T_max, H*D]`` layout, no p
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, List, Optional, Tuple, Union
+from typing import Any, Dict, List, Optional, Tuple, Union
 
 import torch
 
@@ -78,6 +78,35 @@ class BatchState:
 
 
 @dataclass
+class KernelTimeStats:
+    """Reference: gpu_types.py:360-372."""
+
+    count: int
+    total_ms: float
+    avg_ms: float
+    min_ms: float
+    max_ms: float
+
+
+@dataclass
+class PerfStats:
+    """Reference: gpu_types.py:375-384."""
+
+    total_submissions: int
+    kernel_times: Dict[str, KernelTimeStats]
+
+
+@dataclass
+class PerfMonitor:
+    """Reference: gpu_types.py:387-395.  ``kernel_times`` is keyed by the name of the reference
+    function an operation stands for (``kv_cache_update``, ``flash_attention``, ...)."""
+
+    kernel_times: Dict[str, List[float]] = field(default_factory=dict)
+    memory_usage: Dict[str, Any] = field(default_factory=dict)
+    submission_count: int = 0
+
+
+@dataclass
 class GPUContext:
     device: torch.device
     config: GPUConfig
@@ -85,6 +114,7 @@ class GPUContext:
     pipeline_cache: Optional[PipelineCache] = None
     reduction_workspace: Optional[GPUBuffer1D] = None
     dev_status: Optional[torch.Tensor] = None  # int32[1], written by kernels that detect a bad index
+    perf_monitor: Optional[PerfMonitor] = None  # filled by batches opened with enable_profiling
 
 
 @dataclass

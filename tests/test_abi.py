@@ -42,7 +42,7 @@ def test_library_exports_every_declared_symbol(pkg):
 
 def test_status_text_and_version(pkg):
     lib = pkg._native.lib
-    assert lib.b2kv_version() >= 1
+    assert lib.b2kv_version() >= 2
     assert lib.b2kv_strerror(0) == b"ok"
     for code in (-1, -2, -3, -4, -5):
         assert len(lib.b2kv_strerror(code)) > 5
@@ -79,15 +79,15 @@ def test_argument_checks_return_before_any_launch(pkg):
     assert lib.b2kv_decode_paged(A, A, A, A, None, 4, 0, A, 1, 16, 8, 1, 1, 64, 64, 1024, 64, 1024, 0, A, 1 << 20,
                                  None, None) == -1
     # prefill: K cache given without V cache
-    assert lib.b2kv_prefill(A, A, A, A, None, None, A, None, 0, 0, 0, 8, 1, 8, 1, 64, 0, None) == -1
-    assert lib.b2kv_prefill(A, A, A, A, None, None, None, None, 0, 0, 0, 0, 1, 0, 1, 64, 0, None) == -1
+    assert lib.b2kv_prefill(A, A, A, A, None, None, A, None, 0, 0, 0, 8, 1, 8, 1, 64, 0, None, None) == -1
+    assert lib.b2kv_prefill(A, A, A, A, None, None, None, None, 0, 0, 0, 0, 1, 0, 1, 64, 0, None, None) == -1
     # matmul: fp32 is not taken, a missing operand, an inner dimension whose rows are not whole 16-byte chunks,
     # a misaligned residual
-    assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 0, 0, None) == -3
-    assert lib.b2kv_matmul(A, None, None, None, A, 256, 128, 128, 0, 1, None) == -1
-    assert lib.b2kv_matmul(A, A, None, None, A, 256, 100, 128, 0, 1, None) == -3
-    assert lib.b2kv_matmul(A, A, None, A + 2, A, 256, 128, 128, 0, 1, None) == -2
-    assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 2, 1, None) == -1
+    assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 0, 0, None, None) == -3
+    assert lib.b2kv_matmul(A, None, None, None, A, 256, 128, 128, 0, 1, None, None) == -1
+    assert lib.b2kv_matmul(A, A, None, None, A, 256, 100, 128, 0, 1, None, None) == -3
+    assert lib.b2kv_matmul(A, A, None, A + 2, A, 256, 128, 128, 0, 1, None, None) == -2
+    assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 2, 1, None, None) == -1
 
 
 def test_workspace_size_grows_with_the_problem(pkg):

@@ -167,3 +167,50 @@ def test_prefill_into_a_paged_cache_bit_exact_then_decode_continues(pkg, ctx, dt
     tol = U.TOL[dtype]
     np.testing.assert_allclose(U.to_f32(out), U.to_f32(O.reshape(B, N, E)[:, N - 1]), rtol=max(tol["rtol"], 1e-4),
                                atol=tol["atol"])
+
+
+def test_wait_that_runs_out_in_the_tensor_core_kernel_is_reported(pkg, ctx):
+    """The softmax warps of one small launch (a single CTA) are told to behave as if their first
+    barrier wait had run out.  The MMA-issuing thread and the copy thread then run out on their own
+    bounded waits (about two seconds), every warp meets at the common exit, the tensor memory is
+    released and the status word reads B2KV_DEV_WAIT_TIMEOUT, which batch_commit raises.  Nothing
+    faults, and the next launch on the same context is correct."""
+    gpu, native = pkg.gpu, pkg._native
+    B, N, H, D = 1, 256, 1, 128
+    dtype = torch.bfloat16
+    Q = U.randn((B, N, H * D), dtype, ctx.device, 4)
+    K = U.randn((B, N, H * D), dtype, ctx.device, 5)
+    V = U.randn((B, N, H * D), dtype, ctx.device, 6)
+    ctx.config.check_device_status = True
+    native.tune("prefill_test_expire", 1)
+    try:
+        with pytest.raises(RuntimeError, match="bounded wait"):
+            _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, stats=False)
+    finally:
+        native.tune("prefill_test_expire", 0)
+    try:
+        O, _, _ = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, stats=False)
+    finally:
+        ctx.config.check_device_status = False
+    Ow, _, _ = c_oracle.prefill(U.to_oracle(Q.reshape(B * N, H * D)), U.to_oracle(K.reshape(B * N, H * D)),
+                                U.to_oracle(V.reshape(B * N, H * D)), B, N, H, D)
+    np.testing.assert_allclose(U.to_f32(O), Ow, **U.TOL[dtype])
+
+
+def test_profiled_batch_fills_the_perf_monitor(pkg, ctx):
+    """batch_begin(enable_profiling=True): every operation is timed under the reference function's name
+    (simple-llm/src/gpu/gpu_ops.py:245-250, gpu_device.py:569-608)."""
+    gpu = pkg.gpu
+    B, N, H, D = 1, 64, 2, 64
+    Q = U.randn((B, N, H * D), torch.float32, ctx.device, 7)
+    mk = lambda a: U.buf2d(pkg, ctx, a.reshape(B * N, H * D).contiguous())  # noqa: E731
+    Qb, Ob = mk(Q), mk(torch.empty_like(Q))
+    ctx.perf_monitor = None
+    gpu.batch_begin(ctx, enable_profiling=True)
+    gpu.flash_attention(ctx, Qb, Qb, Qb, Ob, None, None, B, N, H, D)
+    gpu.flash_attention(ctx, Qb, Qb, Qb, Ob, None, None, B, N, H, D)
+    gpu.batch_commit(ctx)
+    stats = gpu.perf_monitor_stats_get(ctx.perf_monitor)
+    assert stats.total_submissions == 1
+    fa = stats.kernel_times["flash_attention"]
+    assert fa.count == 2 and 0.0 < fa.min_ms <= fa.max_ms

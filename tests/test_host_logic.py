@@ -131,3 +131,20 @@ def test_buffer_helpers(pkg, ctx):
         gpu.gpu_buffer_2d_create(ctx, 2, 2, np.zeros((2, 2), dtype=np.float64))
     buf = gpu.gpu_buffer_2d_create(ctx, 2, 2, np.arange(4, dtype=np.float32).reshape(2, 2))
     assert buf.shape == (2, 2) and buf.size == 4
+
+
+def test_perf_monitor_mirrors_the_reference(pkg):
+    """simple-llm/src/gpu/gpu_device.py:569-608: record, count, aggregate, reset."""
+    gpu = pkg.gpu
+    mon = gpu.perf_monitor_create()
+    gpu.perf_monitor_kernel_time_record(mon, "kv_cache_update", 0.5)
+    gpu.perf_monitor_kernel_time_record(mon, "kv_cache_update", 1.5)
+    gpu.perf_monitor_kernel_time_record(mon, "flash_attention", 2.0)
+    gpu.perf_monitor_submission_record(mon)
+    stats = gpu.perf_monitor_stats_get(mon)
+    assert stats.total_submissions == 1
+    upd = stats.kernel_times["kv_cache_update"]
+    assert (upd.count, upd.total_ms, upd.avg_ms, upd.min_ms, upd.max_ms) == (2, 2.0, 1.0, 0.5, 1.5)
+    assert stats.kernel_times["flash_attention"].count == 1
+    gpu.perf_monitor_reset(mon)
+    assert gpu.perf_monitor_stats_get(mon).total_submissions == 0 and not mon.kernel_times
