@@ -85,6 +85,9 @@ WORKLOADS = {
                           desc="causal prefill cut to 2 sequences (for profiler captures)"),
     "prefill": dict(kind="prefill", B=8, H=32, D=128, N=4096,
                     desc="causal prefill: B=8 H=32 D=128 N=4096 bf16, fused with the K/V cache write"),
+    "model_step": dict(kind="model_step", B=64, H=32, D=128, lo=512, hi=8192, layers=4, vocab=32768,
+                       desc="one cached decode step of a 4-layer bf16 decoder (E=4096, H=32, vocab 32768): embedding, "
+                            "4 decoder layers, final layernorm, logits, argmax; B=64, len~U[512,8192] seed 0"),
 }
 SLACK = 1024  # rows of head-room above the longest sequence for the appended tokens
 
@@ -930,8 +933,76 @@ def run_prompt_layer(h: Harness, w):
     }
 
 
+def run_model_step(h: Harness, w):
+    """One cached decode step of a whole bf16 decoder on the library's kernels: embedding gather, L decoder
+    layers, final layernorm, logits projection, argmax.  value = generated tokens/s; roofline = HBM over the
+    K/V rows attended plus every weight once."""
+    torch, gpu, ctx = h.torch, h.gpu, h.ctx
+    from llm_experiments_b200 import model
+
+    rank, world, device = h.rank, h.world, h.device
+    B, H, D, L, vocab = w["B"], w["H"], w["D"], w["layers"], w["vocab"]
+    E, T_max = H * D, w["hi"] + 8
+    cfg = model.DecoderConfig(vocab_size=vocab, context_size=T_max, embedding_dim=E, n_heads=H, n_layers=L)
+    weights = model.random_weights(ctx, cfg, seed=6000 + rank)
+    state = model.decoder_state_create(ctx, cfg, weights, batch_size=B, max_seq_len=T_max, ragged=True)
+    lens = make_lengths(w)
+    gen = torch.Generator(device=device).manual_seed(6100 + rank)
+    for c in state.caches:
+        c.layers[0].k_cache.buffer.normal_(generator=gen)
+        c.layers[0].v_cache.buffer.normal_(generator=gen)
+    lens_dev, max_len = torch.from_numpy(lens.astype(np.int32)).to(device), int(lens.max())
+    tokens = torch.randint(0, vocab, (B,), generator=gen, device=device, dtype=torch.int32)
+    tok_b = h.wrap1(tokens)
+    next_b = h.wrap1(torch.empty(B, dtype=torch.int32, device=device))
+
+    def step_device():
+        for c in state.caches:
+            c.seq_lens.copy_(lens_dev)  # every step starts from the same lengths
+            c.current_len = max_len
+        gpu.batch_begin(ctx)
+        model.decode_step(ctx, state, tok_b, next_b)
+        gpu.batch_commit(ctx)
+
+    sampler = h.sampler()
+    m_step = h.measure(step_device)
+    tok_h = tokens.cpu().pin_memory()
+    next_h = torch.empty(B, dtype=torch.int32).pin_memory()
+
+    def step_e2e():
+        gpu.gpu_buffer_1d_write(ctx, tok_h, tok_b)
+        step_device()
+        gpu.gpu_buffer_1d_read(ctx, next_b, next_h)
+
+    m_e2e = h.measure(step_e2e, warmup=1)
+    clocks = sampler.finish()
+    status = int(ctx.dev_status.item()) if ctx.dev_status is not None else 0
+    es = 2
+    kv_bytes = L * int((lens.astype(np.int64) + 1).sum()) * H * D * es * 2
+    weight_bytes = L * 12 * E * E * es + E * vocab * es
+    bytes_step = kv_bytes + weight_bytes
+    peak, _, _, kind = measured_peaks()
+    achieved = bytes_step / (m_step["ms"] * 1e-3) / 1e9
+    launches = model.launches_per_decode_step(cfg)
+    return {
+        "metric": "generated tokens/s (whole cached decode step of the model)", "value": world * B / (m_step["ms"] * 1e-3),
+        "unit": "tokens/s", **spread(m_step), "scaling": "weak", "dtype": "bf16 storage, fp32 arithmetic",
+        "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
+                   "l2": "caches (38 GB) and weights (1.9 GB) far larger than L2, no flush",
+                   "parallelism": f"batch-sharded x{world}, no collective"},
+        "e2e": {"value": world * B / (m_e2e["ms"] * 1e-3), "unit": "tokens/s", **spread(m_e2e),
+                "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4},
+        "gpu_launches": h.steps * h.repeats * launches, "gpu_launches_per_step": launches, "clocks": clocks,
+        "dev_status": status,
+        "roofline": {"bound": "hbm", "kernel": f"the step's {launches} kernels together", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": kind,
+                     "algorithmic_bytes_per_launch": bytes_step, "kv_bytes": kv_bytes, "weight_bytes": weight_bytes,
+                     "traffic": None},
+    }
+
+
 RUNNERS = {"prefill": run_prefill, "qkv": run_qkv_append, "layer_step": run_decode_layer,
-           "prompt_layer": run_prompt_layer}
+           "prompt_layer": run_prompt_layer, "model_step": run_model_step}
 
 
 def run_one(h: Harness, name, **kw):

@@ -58,6 +58,7 @@ extern "C" {
 #define B2KV_DEV_BAD_BLOCK 1    /* block-table entry outside the pool           */
 #define B2KV_DEV_BAD_POSITION 2 /* append position outside [0, T_max)           */
 #define B2KV_DEV_WAIT_TIMEOUT 3 /* a bounded wait on a barrier ran out          */
+#define B2KV_DEV_BAD_TOKEN 4    /* token id outside the embedding table         */
 
 /* Text for a return code.  Replaces the reference's exception messages at the C level. */
 const char* b2kv_strerror(int status);
@@ -250,6 +251,26 @@ int b2kv_layernorm_bf16(const void* x, const void* gamma, const void* beta, void
 int b2kv_extract_last_tokens(const float* in, float* out, int batch_size, int seq_len, int embedding_dim, void* stream);
 int b2kv_softmax(const float* logits, float* probs, int64_t n_rows, int size, void* stream);
 int b2kv_argmax(const float* x, int32_t* out, int n_rows, int size, void* stream);
+/* b2kv_extract_last_tokens and b2kv_argmax on bf16 rows (embedding_dim a multiple of 8): extensions for a bf16
+ * decoder whose hidden rows and logits are bf16. */
+int b2kv_extract_last_tokens_bf16(const void* in, void* out, int batch_size, int seq_len, int embedding_dim, void* stream);
+int b2kv_argmax_bf16(const void* x, int32_t* out, int n_rows, int size, void* stream);
+
+/*
+ * Embedding lookup with the positional encoding added.  Replaces embedding's dispatch
+ * (simple-llm/src/gpu/gpu_pass_forward.py:84-137, kernel src/gpu/gpu_kernels.py:384-449):
+ *   out[b*seq_len + s, :] = table[input_ids[b*seq_len + s], :] + pos_encoding[start_b + s, :]
+ * table is [vocab_size, embedding_dim], pos_encoding [context_size, embedding_dim], out [batch_size*seq_len,
+ * embedding_dim], all of `dtype` (fp32 as in the reference, or bf16 with the sum rounded once); input_ids int32.
+ * The reference always starts at position 0 (start_b = 0: pass seq_pos = NULL, pos0 = 0).  Extension for a cached
+ * decode step, whose one new token per sequence sits at that sequence's current length: start_b = seq_pos[b]
+ * (int32 device array, e.g. the cache's lengths) or the host integer pos0.  embedding_dim a multiple of 8.  A token
+ * id outside the table or a position outside the encoding is clamped and recorded in dev_status
+ * (B2KV_DEV_BAD_TOKEN / B2KV_DEV_BAD_POSITION).
+ */
+int b2kv_embedding(const void* table, const void* pos_encoding, const int32_t* input_ids, const int32_t* seq_pos, int pos0,
+                   void* out, int batch_size, int seq_len, int embedding_dim, int vocab_size, int context_size, int dtype,
+                   int32_t* dev_status, void* stream);
 
 /*
  * Q / K / V projection of one decode step fused with the cache append (bf16 storage, fp32 accumulate).

@@ -26,6 +26,7 @@ DEV_STATUS_TEXT = {
     1: "a block-table entry points outside the pool",
     2: "an append position lies outside the cache",
     3: "a bounded wait on a barrier ran out",
+    4: "a token id lies outside the embedding table",
 }
 
 _vp = ctypes.c_void_p
@@ -60,6 +61,9 @@ SIGNATURES = {
     "b2kv_extract_last_tokens": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "b2kv_softmax": (_i, [_vp, _vp, _i64, _i, _vp]),
     "b2kv_argmax": (_i, [_vp, _vp, _i, _i, _vp]),
+    "b2kv_extract_last_tokens_bf16": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "b2kv_argmax_bf16": (_i, [_vp, _vp, _i, _i, _vp]),
+    "b2kv_embedding": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "b2kv_qkv_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_matmul_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "b2kv_matmul": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),

@@ -10,6 +10,10 @@
 // row is given to 32, 64, 128 or 256 threads by its length, several rows share a CTA, every row is read
 // from HBM once (kept in registers when it fits, re-read from L2 otherwise) and reductions are
 // warp shuffles.  All of them are HBM-bound: 8 bytes per element for layernorm and softmax.
+//
+// The head of a step lives here too: the embedding lookup with the position added
+// (simple-llm/src/gpu/gpu_kernels.py:384-449, one thread per token looping over the row there;
+// here a row is spread over the threads of a CTA in 16-byte chunks).
 #include <math.h>
 
 #include "b2kv_common.cuh"
@@ -183,16 +187,52 @@ __global__ void extract_last_kernel(const float* __restrict__ in, float* __restr
     }
 }
 
+// The same for rows of whole 16-byte chunks of any element type.
+__global__ void extract_last_chunks_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int S, int chunks) {
+    const int b = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < chunks) out[static_cast<int64_t>(b) * chunks + i] = in[(static_cast<int64_t>(b) * S + (S - 1)) * chunks + i];
+}
+
+// out[b*S + s, :] = table[ids[b*S + s], :] + pos_enc[start_b + s, :], start_b = seq_pos[b] (or `pos0`).
+// One CTA per token; four elements per thread and pass.  A token id outside the table or a position
+// outside the encoding is clamped and recorded in the status word instead of being read.
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads)
+embedding_kernel(const T* __restrict__ table, const T* __restrict__ pos_enc, const int32_t* __restrict__ ids,
+                 const int32_t* __restrict__ seq_pos, int pos0, T* __restrict__ out, int S, int E, int vocab, int context,
+                 int32_t* dev_status) {
+    const int64_t tok = blockIdx.x;
+    const int b = static_cast<int>(tok / S), s = static_cast<int>(tok - static_cast<int64_t>(b) * S);
+    int id = ids[tok];
+    int pos = (seq_pos ? seq_pos[b] : pos0) + s;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) report_status(dev_status, B2KV_DEV_BAD_TOKEN);
+        id = 0;
+    }
+    if (pos < 0 || pos >= context) {
+        if (threadIdx.x == 0) report_status(dev_status, B2KV_DEV_BAD_POSITION);
+        pos = pos < 0 ? 0 : context - 1;
+    }
+    const T* tr = table + static_cast<int64_t>(id) * E;
+    const T* pr = pos_enc + static_cast<int64_t>(pos) * E;
+    T* yr = out + tok * E;
+    for (int i = threadIdx.x; i < E / 4; i += kCtaThreads) {
+        const float4 a = load4(tr, i), c = load4(pr, i);
+        store4(yr, i, make_float4(a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w));
+    }
+}
+
 // Index of the largest value of each row (the lowest index among equals, like numpy.argmax).
-__global__ void __launch_bounds__(kCtaThreads) argmax_kernel(const float* __restrict__ x, int32_t* __restrict__ out,
-                                                            int V) {
+template <typename T>
+__global__ void __launch_bounds__(kCtaThreads) argmax_kernel(const T* __restrict__ x, int32_t* __restrict__ out, int V) {
     __shared__ float s_val[kCtaThreads / 32];
     __shared__ int s_idx[kCtaThreads / 32];
-    const float* xr = x + static_cast<int64_t>(blockIdx.x) * V;
+    const T* xr = x + static_cast<int64_t>(blockIdx.x) * V;
     float best = -INFINITY;
     int idx = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += kCtaThreads) {
-        const float v = xr[i];
+        const float v = Elt<T>::to_float(xr[i]);
         if (v > best || (v == best && i < idx)) best = v, idx = i;
     }
     auto merge = [&](float ov, int oi) {
@@ -255,7 +295,57 @@ extern "C" int b2kv_extract_last_tokens(const float* in, float* out, int batch_s
 extern "C" int b2kv_argmax(const float* x, int32_t* out, int n_rows, int size, void* stream) {
     if (!x || !out) return B2KV_ERR_BAD_ARG;
     if (n_rows <= 0 || size <= 0) return B2KV_ERR_BAD_ARG;
-    argmax_kernel<<<n_rows, kCtaThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, size);
+    argmax_kernel<float><<<n_rows, kCtaThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, size);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
+extern "C" int b2kv_argmax_bf16(const void* x, int32_t* out, int n_rows, int size, void* stream) {
+    if (!x || !out) return B2KV_ERR_BAD_ARG;
+    if (n_rows <= 0 || size <= 0) return B2KV_ERR_BAD_ARG;
+    argmax_kernel<__nv_bfloat16><<<n_rows, kCtaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), out, size);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
+extern "C" int b2kv_extract_last_tokens_bf16(const void* in, void* out, int batch_size, int seq_len, int embedding_dim,
+                                             void* stream) {
+    if (!in || !out) return B2KV_ERR_BAD_ARG;
+    if (batch_size <= 0 || seq_len <= 0 || embedding_dim <= 0) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(in) || !aligned16(out)) return B2KV_ERR_ALIGN;
+    if (batch_size > 65535 || embedding_dim % 8 != 0) return B2KV_ERR_UNSUPPORTED;
+    const int chunks = embedding_dim / 8;
+    const dim3 grid((chunks + 255) / 256, batch_size);
+    extract_last_chunks_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(in), static_cast<uint4*>(out), seq_len, chunks);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
+extern "C" int b2kv_embedding(const void* table, const void* pos_encoding, const int32_t* input_ids,
+                              const int32_t* seq_pos, int pos0, void* out, int batch_size, int seq_len, int embedding_dim,
+                              int vocab_size, int context_size, int dtype, int32_t* dev_status, void* stream) {
+    if (elt_bytes(dtype) == 0) return B2KV_ERR_UNSUPPORTED;
+    if (!table || !pos_encoding || !input_ids || !out) return B2KV_ERR_BAD_ARG;
+    if (batch_size <= 0 || seq_len <= 0 || embedding_dim <= 0 || vocab_size <= 0 || context_size <= 0 || pos0 < 0)
+        return B2KV_ERR_BAD_ARG;
+    if (!aligned16(table) || !aligned16(pos_encoding) || !aligned16(out)) return B2KV_ERR_ALIGN;
+    if (embedding_dim % 8 != 0) return B2KV_ERR_UNSUPPORTED;  // rows of whole 16-byte chunks in either type
+    const long long tokens = static_cast<long long>(batch_size) * seq_len;
+    if (tokens > 0x7fffffffLL) return B2KV_ERR_UNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = static_cast<unsigned>(tokens);
+    if (dtype == B2KV_DTYPE_F32) {
+        embedding_kernel<float><<<grid, kCtaThreads, 0, s>>>(
+            static_cast<const float*>(table), static_cast<const float*>(pos_encoding), input_ids, seq_pos, pos0,
+            static_cast<float*>(out), seq_len, embedding_dim, vocab_size, context_size, dev_status);
+    } else {
+        using T = __nv_bfloat16;
+        embedding_kernel<T><<<grid, kCtaThreads, 0, s>>>(static_cast<const T*>(table), static_cast<const T*>(pos_encoding),
+                                                        input_ids, seq_pos, pos0, static_cast<T*>(out), seq_len,
+                                                        embedding_dim, vocab_size, context_size, dev_status);
+    }
     B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
 }

@@ -30,7 +30,7 @@ from .kv_cache import (
     kv_cache_update,
 )
 from .projection import matmul, qkv_project_append
-from .step_tail import argmax, extract_last_tokens, layernorm, softmax
+from .step_tail import argmax, embedding, extract_last_tokens, layernorm, softmax
 from .types import GPUBuffer1D, GPUBuffer2D, GPUConfig, GPUContext, KVCache, KVCacheConfig, KVCacheLayer
 
 __all__ = [
@@ -44,6 +44,6 @@ __all__ = [
     "perf_monitor_submission_record",
     "kv_cache_create", "kv_cache_reset", "kv_cache_update", "attention_with_kv_cache",
     "kv_cache_gather", "kv_cache_set_lengths",
-    "layernorm", "extract_last_tokens", "softmax", "argmax",
+    "embedding", "layernorm", "extract_last_tokens", "softmax", "argmax",
     "qkv_project_append", "matmul",
 ]

@@ -128,3 +128,49 @@ def test_layernorm_bf16_rows_vs_oracle(pkg, ctx, n, size):
     gpu.batch_commit(ctx)
     want = T.layernorm(U.to_f32(x), U.to_f32(gamma), U.to_f32(beta))
     np.testing.assert_allclose(U.to_f32(out), want, rtol=2.0 ** -8, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_lookup_with_positions(pkg, ctx, dtype):
+    """Reference kernel simple-llm/src/gpu/gpu_kernels.py:384-449: table row + position row, positions restarting
+    at 0 in every sequence; extension: per-sequence start positions.  One rounding of the fp32 sum."""
+    gpu = pkg.gpu
+    V, C, E, B, S = 50, 40, 72, 3, 11
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn((V, E), generator=g).to(dtype)
+    pos = torch.randn((C, E), generator=g).to(dtype)
+    ids = torch.randint(0, V, (B * S,), generator=g, dtype=torch.int32)
+    mk2 = lambda t: gpu.GPUBuffer2D(buffer=t.to(ctx.device), shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    mk1 = lambda t: gpu.GPUBuffer1D(buffer=t.to(ctx.device), shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    out = mk2(torch.empty((B * S, E), dtype=dtype))
+    gpu.batch_begin(ctx)
+    gpu.embedding(ctx, mk2(table), mk2(pos), mk1(ids), out, B, S)
+    gpu.batch_commit(ctx)
+    where = torch.arange(S).repeat(B)
+    want = (table[ids.long()].float() + pos[where].float()).to(dtype)
+    assert torch.equal(out.buffer.cpu(), want)
+    # one new token per sequence at that sequence's own position
+    starts = torch.tensor([0, 39, 17], dtype=torch.int32)
+    out1 = mk2(torch.empty((B, E), dtype=dtype))
+    gpu.batch_begin(ctx)
+    gpu.embedding(ctx, mk2(table), mk2(pos), mk1(ids[:B].contiguous()), out1, B, 1, start_pos=starts.to(ctx.device))
+    gpu.batch_commit(ctx)
+    want1 = (table[ids[:B].long()].float() + pos[starts.long()].float()).to(dtype)
+    assert torch.equal(out1.buffer.cpu(), want1)
+
+
+def test_embedding_reports_ids_outside_the_table(pkg, ctx):
+    gpu = pkg.gpu
+    mk2 = lambda t: gpu.GPUBuffer2D(buffer=t.to(ctx.device), shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    mk1 = lambda t: gpu.GPUBuffer1D(buffer=t.to(ctx.device), shape=tuple(t.shape), size=t.numel())  # noqa: E731
+    table, pos = torch.ones((4, 8)), torch.zeros((4, 8))
+    out = mk2(torch.empty((2, 8)))
+    ctx.config.check_device_status = True
+    try:
+        gpu.batch_begin(ctx)
+        gpu.embedding(ctx, mk2(table), mk2(pos), mk1(torch.tensor([1, 9], dtype=torch.int32)), out, 2, 1)
+        with pytest.raises(RuntimeError, match="embedding table"):
+            gpu.batch_commit(ctx)
+    finally:
+        ctx.config.check_device_status = False
+    assert torch.equal(out.buffer.cpu(), torch.ones((2, 8)))  # the bad id was clamped to row 0, nothing faulted

@@ -148,3 +148,24 @@ def test_perf_monitor_mirrors_the_reference(pkg):
     assert stats.kernel_times["flash_attention"].count == 1
     gpu.perf_monitor_reset(mon)
     assert gpu.perf_monitor_stats_get(mon).total_submissions == 0 and not mon.kernel_times
+
+
+def test_embedding_checks_like_the_reference(pkg, ctx):
+    """simple-llm/src/gpu/gpu_pass_forward.py:110-128."""
+    gpu = pkg.gpu
+    table = gpu.gpu_buffer_2d_create(ctx, 10, 16)
+    pos = gpu.gpu_buffer_2d_create(ctx, 6, 16)
+    ids = gpu.gpu_buffer_1d_create(ctx, 8, dtype=torch.int32)
+    out = gpu.gpu_buffer_2d_create(ctx, 8, 16)
+    with pytest.raises(ValueError, match="Invalid batch_size=0 or seq_len=4"):
+        gpu.embedding(ctx, table, pos, ids, out, 0, 4)
+    with pytest.raises(ValueError, match="Embedding dimension mismatch: table has 16, pos_encoding has 8"):
+        gpu.embedding(ctx, table, gpu.gpu_buffer_2d_create(ctx, 6, 8), ids, out, 2, 4)
+    with pytest.raises(ValueError, match="Sequence length 7 exceeds context size 6"):
+        gpu.embedding(ctx, table, pos, ids, out, 2, 7)
+    with pytest.raises(ValueError, match="input_ids shape mismatch"):
+        gpu.embedding(ctx, table, pos, gpu.gpu_buffer_1d_create(ctx, 7, dtype=torch.int32), out, 2, 4)
+    with pytest.raises(ValueError, match="output shape mismatch"):
+        gpu.embedding(ctx, table, pos, ids, gpu.gpu_buffer_2d_create(ctx, 8, 8), 2, 4)
+    with pytest.raises(RuntimeError, match="batch_begin"):
+        gpu.embedding(ctx, table, pos, ids, out, 2, 4)

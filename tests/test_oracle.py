@@ -166,3 +166,27 @@ def test_prompt_layer_oracle_agrees_with_the_decode_layer_oracle_on_the_last_tok
     y_last, k_new, _ = o.decoder_layer_step(x[last], w, ks, vs, np.full(B, N - 1), H)
     np.testing.assert_allclose(y_last, y[last], rtol=0, atol=1e-6)
     np.testing.assert_array_equal(k_new, k[last])
+
+
+def test_model_oracle_cached_step_equals_longer_prompt():
+    """The stacked-layer decoder oracle agrees with itself: a cached decode step after a prompt of N tokens gives
+    the logits of the last position of the same N + 1 tokens run as one prompt (up to bf16 rounding of the
+    intermediate rows, which the two paths round at the same places)."""
+    from oracle import model_oracle
+    from oracle.decode_layer_oracle import bf16_round
+
+    rs = np.random.RandomState(0)
+    E, V, H, L, N, B = 64, 96, 2, 2, 7, 2
+    r = lambda shape, s=1.0: bf16_round((rs.randn(*shape) * s).astype(np.float32))  # noqa: E731
+    layer = lambda: dict(ln1_gamma=r((E,), 0.1) + 1, ln1_beta=r((E,), 0.1), wq=r((E, E), E ** -0.5),  # noqa: E731
+                         wk=r((E, E), E ** -0.5), wv=r((E, E), E ** -0.5), wo=r((E, E), E ** -0.5),
+                         ln2_gamma=r((E,), 0.1) + 1, ln2_beta=r((E,), 0.1), w1=r((E, 4 * E), E ** -0.5),
+                         b1=r((4 * E,), 0.1), w2=r((4 * E, E), (4 * E) ** -0.5), b2=r((E,), 0.1))
+    params = dict(embedding=r((V, E)), pos_encoding=r((N + 1, E)), layers=[layer() for _ in range(L)],
+                  lnf_gamma=r((E,), 0.1) + 1, lnf_beta=r((E,), 0.1), out_proj=r((E, V), E ** -0.5))
+    ids = rs.randint(0, V, size=(B, N + 1))
+    _, cache = model_oracle.prefill(params, ids[:, :N].reshape(-1), B, N, H)
+    stepped = model_oracle.decode_step(params, ids[:, N], cache, H)
+    whole, _ = model_oracle.prefill(params, ids.reshape(-1), B, N + 1, H)
+    assert len(cache[0][0][0]) == N + 1
+    np.testing.assert_allclose(stepped, whole, rtol=0, atol=4e-2)
