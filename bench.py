@@ -30,7 +30,7 @@ headline loops (each cache is freed before the next is built):
 * with N > 1: ``parity_multi`` (a small head-split decode gathered with NCCL and with the
   peer stores of the merge kernel, and a sequence-split decode, each checked on rank 0 against
   the CPU oracle outside every timed region), ``workloads.decode_strong`` (the 64 sequences cut
-  into contiguous slices of 64 / N, no collective) and ``workloads.longctx_headsplit`` (the long
+  into N sets of 64 / N, as contiguous slices and balanced by the tokens attended, no collective) and ``workloads.longctx_headsplit`` (the long
   context with its heads split over the GPUs, outputs gathered by NCCL and by the fused peer
   stores).
 
@@ -316,7 +316,7 @@ def fill_normal(torch, buf, gen, dtype):
 # decode workloads (contiguous, paged, long context, batch-sharded, head-split)
 # ------------------------------------------------------------------------------------------
 
-def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False):
+def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False, assign="contiguous"):
     """Append + decode over one layer's cache.  Returns the record of the workload (every rank computes it; the
     figures are maxima over ranks)."""
     torch, gpu, ctx = h.torch, h.gpu, h.ctx
@@ -332,8 +332,11 @@ def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False):
         h0, h1 = sharding.head_range(H_total, rank, world)  # this rank's heads of every sequence
         H = h1 - h0
     if strong:
-        b0, b1 = sharding.shard_range(B_total, rank, world)  # this rank's contiguous slice of the sequences
-        B, lens0 = b1 - b0, lens_all[b0:b1]
+        if assign == "balanced":  # sequences dealt so that every rank attends about the same number of tokens
+            mine = sharding.balanced_assignment(lens_all, world)[rank]
+        else:  # this rank's contiguous slice of the sequences
+            mine = list(range(*sharding.shard_range(B_total, rank, world)))
+        B, lens0 = len(mine), lens_all[mine]
     E = H * D
     dtype = torch.bfloat16
     steps = h.steps
@@ -430,7 +433,9 @@ def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False):
                + ("by peer stores fused into the merge kernel" if fused is not None
                   else "with one NCCL all-gather per step"))
     elif strong:
-        par = f"the batch cut into contiguous slices of {B_total}/{world} sequences, no collective in the step"
+        par = (f"the batch cut into {world} sets of {B_total}/{world} sequences ("
+               + ("balanced by tokens attended" if assign == "balanced" else "contiguous slices")
+               + "), no collective in the step")
     else:
         par = f"batch-sharded x{world}, no collective in the step"
     rec = {
@@ -1040,11 +1045,13 @@ def run_b200(args):
         for sub in ("paged", "prefill", "longctx"):
             subs[sub] = sub_record(run_one, h, sub)
         if world > 1:
-            strong = sub_record(run_one, h, "decode_strong")
-            if "ms_per_step" in strong:
-                strong["speedup_vs_one_gpu"] = head["ms_per_step"] / strong["ms_per_step"]
-                strong["efficiency"] = strong["speedup_vs_one_gpu"] / world
-            subs["decode_strong"] = strong
+            subs["decode_strong"] = {}
+            for assign in ("contiguous", "balanced"):
+                strong = sub_record(run_one, h, "decode_strong", assign=assign)
+                if "ms_per_step" in strong:
+                    strong["speedup_vs_one_gpu"] = head["ms_per_step"] / strong["ms_per_step"]
+                    strong["efficiency"] = strong["speedup_vs_one_gpu"] / world
+                subs["decode_strong"][assign] = strong
             hs = {}
             for how in ("nccl", "fused"):
                 r = sub_record(run_one, h, "longctx_headsplit", gather=how)

@@ -5,8 +5,9 @@ has no counterpart there.  Every (sequence, head) pair is independent in append,
 prefill (one workgroup per pair in the reference kernels, simple-llm/src/gpu/gpu_kernels.py:2838-2839
 and :612-614), which gives two ways to cut the work:
 
-* **batch sharding** (default): rank r owns a contiguous slice of the sequences together with
-  their cache; a step needs no communication at all.
+* **batch sharding** (default): rank r owns a contiguous slice of the sequences (``shard_range``), or a set
+  chosen so that the ranks attend equally many tokens (``balanced_assignment``), together with their
+  cache; a step needs no communication at all.
 * **head splitting** (long contexts with few sequences): rank r owns heads ``[r*H/W, (r+1)*H/W)`` of
   every sequence; after the local decode the ranks exchange their ``[B, H/W * D]`` outputs with
   one all-gather (NCCL over NVLink on GPUs, gloo in CPU tests) and interleave them back to
@@ -17,7 +18,7 @@ ranks in tests.
 """
 from __future__ import annotations
 
-from typing import Callable, Tuple
+from typing import Callable, List, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -30,6 +31,24 @@ def shard_range(total: int, rank: int, world: int) -> Tuple[int, int]:
     base, extra = divmod(total, world)
     start = rank * base + min(rank, extra)
     return start, start + base + (1 if rank < extra else 0)
+
+
+def balanced_assignment(lengths: Sequence[int], world: int) -> List[List[int]]:
+    """Sequences for every rank such that the ranks attend about the same number of tokens: longest sequence
+    first, each to the rank with the fewest tokens so far among those that still have room (every rank gets
+    ``len(lengths) // world`` sequences, the first ``len(lengths) % world`` ranks one more).  A decode step
+    is as slow as its heaviest rank, and contiguous slices of a ragged batch can differ by a quarter."""
+    if world <= 0:
+        raise ValueError(f"bad world: {world}")
+    n = len(lengths)
+    room = [n // world + (1 if r < n % world else 0) for r in range(world)]
+    load = [0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for i in sorted(range(n), key=lambda i: (-int(lengths[i]), i)):
+        r = min((r for r in range(world) if len(out[r]) < room[r]), key=lambda r: (load[r], r))
+        out[r].append(i)
+        load[r] += int(lengths[i])
+    return [sorted(ids) for ids in out]
 
 
 def head_range(n_heads: int, rank: int, world: int) -> Tuple[int, int]:
@@ -199,13 +218,21 @@ def merge_partials(ctx, parts: torch.Tensor, batch: int, n_heads: int, head_dim:
     return out
 
 
+def exchange_partials(part: torch.Tensor, merge: Callable[[torch.Tensor], torch.Tensor], group=None) -> torch.Tensor:
+    """The exchange of the sequence-split decode: all-gathers every rank's ``[B*H, D + 2]`` float partials
+    and hands the ``[world, B*H, D + 2]`` stack to `merge`, whose result is returned.  The merge is passed in
+    as a callable so that the exchange runs unchanged on CPU ranks in tests."""
+    world = dist.get_world_size(group)
+    gathered = torch.empty((world * part.shape[0], part.shape[1]), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(gathered, part.contiguous(), group=group)
+    return merge(gathered.reshape(world, part.shape[0], part.shape[1]))
+
+
 def sequence_split_decode(ctx, cache, layer_idx: int, q_new, group=None) -> torch.Tensor:
     """Decode step when each rank caches a different slice of every sequence's tokens (all heads):
     local unnormalised attention, one all-gather of the ``[B*H, D + 2]`` float partials, merge.
     Returns the full ``[B, H*D]`` output on every rank."""
-    world = dist.get_world_size(group)
     part = decode_partial(ctx, cache, layer_idx, q_new)
-    gathered = torch.empty((world * part.shape[0], part.shape[1]), dtype=part.dtype, device=part.device)
-    dist.all_gather_into_tensor(gathered, part, group=group)
-    return merge_partials(ctx, gathered.reshape(world, part.shape[0], part.shape[1]), cache.batch_size, cache.n_heads,
-                          cache.head_dim, cache.dtype)
+    return exchange_partials(
+        part, lambda parts: merge_partials(ctx, parts, cache.batch_size, cache.n_heads, cache.head_dim, cache.dtype),
+        group)
