@@ -230,6 +230,20 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
                  int D, int dtype, int32_t* dev_status, void* stream);
 
 /*
+ * b2kv_prefill into a PAGED cache (no counterpart in the reference, whose cache is contiguous): the prompt's K / V
+ * rows 0..N-1 of sequence b go to the pool blocks that block_table[b, :] names, addressed as in b2kv_append_paged.
+ * On the tensor-core path (bf16, D == 128 or 64) the attention kernel stores every whole block itself from its
+ * shared-memory tiles when block_size is a multiple of 8 that divides 128 or is a multiple of 128; a last, partly
+ * filled block, other block sizes and the SIMT path are written by a copy kernel behind the attention.  No row past
+ * N - 1 is written and no length is advanced.  A table entry outside [0, n_blocks) is skipped and recorded in
+ * dev_status (B2KV_DEV_BAD_BLOCK).
+ */
+int b2kv_prefill_paged(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_pool, void* v_pool,
+                       const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int64_t stride_blk,
+                       int64_t stride_t, int64_t stride_h, int B, int N, int H, int D, int dtype, int32_t* dev_status,
+                       void* stream);
+
+/*
  * The tail of a cached generation step, fp32 like the reference's buffers.  Each replaces one
  * dispatch of simple-llm/src/gpu/gpu_pass_forward.py:
  *   b2kv_layernorm            layernorm :140-176 (WGSL src/gpu/gpu_kernels.py:137-249): per row of
@@ -318,7 +332,8 @@ int b2kv_matmul(const void* a, const void* w, const void* bias, const void* resi
  * another thread is inside a b2kv call): sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,
- * N a multiple of 256, "prefill_test_expire": 1 = test hook, the softmax warps of the one-CTA tensor-core prefill
+ * N a multiple of 256, "prefill_unfused_paged": 1 = b2kv_prefill_paged always
+ * fills the pool with the copy kernel, "prefill_test_expire": 1 = test hook, the softmax warps of the one-CTA tensor-core prefill
  * behave as if their first bounded wait had run out (the launch then ends after about two seconds with
  * B2KV_DEV_WAIT_TIMEOUT in dev_status), "matmul_splits": ranges of input features per tile in b2kv_matmul_rows,
  * "gemm_variant": 1 = one CTA per output tile, 2 / 3 = CTA pairs with 64 / 128 input features per

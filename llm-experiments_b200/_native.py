@@ -56,6 +56,8 @@ SIGNATURES = {
     "b2kv_merge_partials": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "b2kv_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "b2kv_prefill_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i,
+                                _vp, _vp]),
     "b2kv_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),
     "b2kv_layernorm_bf16": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),
     "b2kv_extract_last_tokens": (_i, [_vp, _vp, _i, _i, _i, _vp]),

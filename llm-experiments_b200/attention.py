@@ -4,8 +4,8 @@ Mirrors simple-llm/src/gpu/gpu_pass_forward.py:497-588: same positional argument
 checks and ``ValueError`` texts (:531-555), ``None`` returned, O / L / M written in place.
 ``flash_attn_bc`` / ``flash_attn_br`` are ignored (the CUDA kernels choose their own tiles).
 Extension: ``cache`` / ``layer_idx`` also write K and V rows 0..N-1 of every sequence into
-that cache layer (in the same kernel for a contiguous cache, through the block table by a copy
-kernel behind it for a paged one) and set the cache length to N, which the reference can only
+that cache layer (in the same kernel for a contiguous cache and for the whole blocks of a paged one
+on the tensor-core path; through the block table by a copy kernel behind it otherwise) and set the cache length to N, which the reference can only
 do token by token through ``kv_cache_update``.
 """
 from __future__ import annotations
@@ -67,19 +67,20 @@ def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffe
             t_max = cache.max_seq_len
 
     stream = batch_op_begin(ctx)
-    rc = _native.lib.b2kv_prefill(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(), O.buffer.data_ptr(),
-                                  None if L is None else L.buffer.data_ptr(),
-                                  None if M is None else M.buffer.data_ptr(), kc, vc, s0, st, sh, t_max, batch_size,
-                                  seq_len, n_heads, head_dim, dtype_code(dtype), dev_status_ptr(ctx), stream)
-    _native.check(rc)
+    lm = (None if L is None else L.buffer.data_ptr(), None if M is None else M.buffer.data_ptr())
     if cache is not None and cache.block_table is not None:
-        # paged: the prompt's rows are scattered through the block table by a copy kernel behind the attention
-        rc = _native.lib.b2kv_append_rows_paged(K.buffer.data_ptr(), V.buffer.data_ptr(), layer.k_cache.buffer.data_ptr(),
-                                                layer.v_cache.buffer.data_ptr(), cache.block_table.data_ptr(),
-                                                cache.block_table.shape[1], cache.block_size, cache.n_blocks, batch_size,
-                                                seq_len, 0, n_heads, head_dim, s0, st, sh, dtype_code(dtype),
-                                                dev_status_ptr(ctx), stream)
-        _native.check(rc)
+        # paged: whole blocks are stored by the attention kernel, the rest by a copy kernel behind it
+        rc = _native.lib.b2kv_prefill_paged(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(),
+                                            O.buffer.data_ptr(), *lm, layer.k_cache.buffer.data_ptr(),
+                                            layer.v_cache.buffer.data_ptr(), cache.block_table.data_ptr(),
+                                            cache.block_table.shape[1], cache.block_size, cache.n_blocks, s0, st, sh,
+                                            batch_size, seq_len, n_heads, head_dim, dtype_code(dtype),
+                                            dev_status_ptr(ctx), stream)
+    else:
+        rc = _native.lib.b2kv_prefill(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(), O.buffer.data_ptr(),
+                                      *lm, kc, vc, s0, st, sh, t_max, batch_size, seq_len, n_heads, head_dim,
+                                      dtype_code(dtype), dev_status_ptr(ctx), stream)
+    _native.check(rc)
     if cache is not None:
         cache.current_len = seq_len
         if cache.seq_lens is not None:

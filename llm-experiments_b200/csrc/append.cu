@@ -68,16 +68,16 @@ __global__ void __launch_bounds__(1024) append_kernel(const uint4* __restrict__ 
     }
 }
 
-// Many rows per sequence (a prompt): grid (n_rows, B); rows[b * n_rows + i] goes to position first_pos + i
-// of sequence b.  Same addressing as append_kernel; nothing is advanced.
+// Many rows per sequence (a prompt): grid (n_rows, B); rows[b * src_rows_per_seq + src_first + i] goes to position
+// first_pos + i of sequence b.  Same addressing as append_kernel; nothing is advanced.
 __global__ void __launch_bounds__(512) append_rows_kernel(const uint4* __restrict__ k_rows, const uint4* __restrict__ v_rows,
                                                           uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, RowMap m,
-                                                          int n_rows, int first_pos, int H, int D, int chunks_per_row,
-                                                          int shift) {
+                                                          int src_rows_per_seq, int src_first, int first_pos, int H, int D,
+                                                          int chunks_per_row, int shift) {
     const int b = blockIdx.y, i = blockIdx.x;
     const int64_t base = row_offset(m, b, first_pos + i);
     if (base < 0) return;
-    const int64_t src0 = (static_cast<int64_t>(b) * n_rows + i) * chunks_per_row;
+    const int64_t src0 = (static_cast<int64_t>(b) * src_rows_per_seq + src_first + i) * chunks_per_row;
     for (int idx = threadIdx.x; idx < chunks_per_row; idx += blockDim.x) {
         const int e = idx << shift;
         const int h = e / D, d = e - h * D;
@@ -148,6 +148,32 @@ static int launch_gather(const void* cache, void* out, RowMap m, int B, int H, i
     return B2KV_OK;
 }
 
+int append_rows_paged_from(const void* k_rows, const void* v_rows, void* k_pool, void* v_pool, const int32_t* block_table,
+                           int max_blocks, int block_size, int n_blocks, int B, int n_rows, int first_pos,
+                           int src_rows_per_seq, int src_first, int H, int D, int64_t stride_blk, int64_t stride_t,
+                           int64_t stride_h, int dtype, int32_t* dev_status, void* stream) {
+    int rc = check_common(B, H, D, dtype, stride_blk, stride_t, stride_h);
+    if (rc != B2KV_OK) return rc;
+    if (!k_rows || !v_rows || !k_pool || !v_pool) return B2KV_ERR_BAD_ARG;
+    if (!block_table || max_blocks <= 0 || block_size <= 0 || n_blocks <= 0) return B2KV_ERR_BAD_ARG;
+    if (n_rows <= 0 || first_pos < 0 || static_cast<long long>(first_pos) + n_rows > static_cast<long long>(max_blocks) * block_size)
+        return B2KV_ERR_BAD_ARG;
+    if (src_first < 0 || src_first + n_rows > src_rows_per_seq) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(k_rows) || !aligned16(v_rows) || !aligned16(k_pool) || !aligned16(v_pool)) return B2KV_ERR_ALIGN;
+    if (B > 65535) return B2KV_ERR_UNSUPPORTED;
+    RowMap m{nullptr, 0, block_table, max_blocks, block_size, n_blocks, stride_blk, stride_t, stride_h, 0, dev_status};
+    const int es = elt_bytes(dtype);
+    const int chunks = H * D * es / 16;
+    const int shift = es == 4 ? 2 : 3;
+    int threads = (chunks + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    append_rows_kernel<<<dim3(n_rows, B), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(k_rows), static_cast<const uint4*>(v_rows), static_cast<uint4*>(k_pool),
+        static_cast<uint4*>(v_pool), m, src_rows_per_seq, src_first, first_pos, H, D, chunks, shift);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
 }  // namespace b2kv
 
 using namespace b2kv;
@@ -181,25 +207,8 @@ int b2kv_append_rows_paged(const void* k_rows, const void* v_rows, void* k_pool,
                            int max_blocks, int block_size, int n_blocks, int B, int n_rows, int first_pos, int H, int D,
                            int64_t stride_blk, int64_t stride_t, int64_t stride_h, int dtype, int32_t* dev_status,
                            void* stream) {
-    int rc = check_common(B, H, D, dtype, stride_blk, stride_t, stride_h);
-    if (rc != B2KV_OK) return rc;
-    if (!k_rows || !v_rows || !k_pool || !v_pool) return B2KV_ERR_BAD_ARG;
-    if (!block_table || max_blocks <= 0 || block_size <= 0 || n_blocks <= 0) return B2KV_ERR_BAD_ARG;
-    if (n_rows <= 0 || first_pos < 0 || static_cast<long long>(first_pos) + n_rows > static_cast<long long>(max_blocks) * block_size)
-        return B2KV_ERR_BAD_ARG;
-    if (!aligned16(k_rows) || !aligned16(v_rows) || !aligned16(k_pool) || !aligned16(v_pool)) return B2KV_ERR_ALIGN;
-    if (B > 65535) return B2KV_ERR_UNSUPPORTED;
-    RowMap m{nullptr, 0, block_table, max_blocks, block_size, n_blocks, stride_blk, stride_t, stride_h, 0, dev_status};
-    const int es = elt_bytes(dtype);
-    const int chunks = H * D * es / 16;
-    const int shift = es == 4 ? 2 : 3;
-    int threads = (chunks + 31) / 32 * 32;
-    if (threads > 512) threads = 512;
-    append_rows_kernel<<<dim3(n_rows, B), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(k_rows), static_cast<const uint4*>(v_rows), static_cast<uint4*>(k_pool),
-        static_cast<uint4*>(v_pool), m, n_rows, first_pos, H, D, chunks, shift);
-    B2KV_CUDA_TRY(cudaGetLastError());
-    return B2KV_OK;
+    return append_rows_paged_from(k_rows, v_rows, k_pool, v_pool, block_table, max_blocks, block_size, n_blocks, B, n_rows,
+                                  first_pos, n_rows, 0, H, D, stride_blk, stride_t, stride_h, dtype, dev_status, stream);
 }
 
 int b2kv_gather(const void* cache, void* out, const int32_t* seq_lens, int len, int B, int H, int D, int T_out,

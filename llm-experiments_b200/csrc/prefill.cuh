@@ -17,6 +17,11 @@ struct PrefillParams {
     int64_t stride_b, stride_t, stride_h;
     int B, N, H;
     float q_prescale;
+    // paged cache (tensor-core kernel): k_cache / v_cache are block pools and the prompt's rows go through the table
+    const int32_t* block_table;  // [B, max_blocks], null for a contiguous cache
+    int max_blocks, block_size, n_blocks;
+    int rows_per_store;  // rows of one TMA store into a pool block: min(block_size, 128)
+    int n_whole;         // tokens covered by whole blocks (N rounded down to a multiple of block_size)
     int32_t* dev_status;  // optional status word: receives B2KV_DEV_WAIT_TIMEOUT when a bounded wait ran out
     int test_expire;      // test hook: the softmax warps of the one-CTA tensor-core kernel give up before their first wait
     int group;  // tensor-core kernel: (sequence, head) pairs whose row blocks are launched next to each other; 0 = by size, < 0 = all

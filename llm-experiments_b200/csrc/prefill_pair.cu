@@ -578,7 +578,7 @@ static bool make_map(CUtensorMap* map, const void* base, int B, int N, int E, in
 int prefill_tensor_core_pair(const PrefillParams& p_in, int D, int dtype, void* stream) {
     PrefillParams p = p_in;
     if (p.group == 0) p.group = static_cast<int>(std::max<long long>(1, (32LL << 20) / (4LL * p.N * pair::kD)));
-    if (dtype != B2KV_DTYPE_BF16 || D != pair::kD) return B2KV_ERR_UNSUPPORTED;
+    if (dtype != B2KV_DTYPE_BF16 || D != pair::kD || p.block_table != nullptr) return B2KV_ERR_UNSUPPORTED;
     if (p.N < 2 * pair::kRows || p.N % (2 * pair::kRows) != 0) return B2KV_ERR_UNSUPPORTED;
     const int E = p.H * D;
     const long long ctas = 2LL * (p.N / (2 * pair::kRows)) * p.H * p.B;

@@ -236,8 +236,8 @@ extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O
         if (!stride_ok(stride_b, es) || !stride_ok(stride_t, es) || !stride_ok(stride_h, es)) return B2KV_ERR_ALIGN;
     }
     PrefillParams p{Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, B, N, H,
-                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), dev_status,
-                    tune_get("prefill_test_expire"), tune_get("prefill_group")};
+                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), nullptr, 0, 0, 0, 0, 0,
+                    dev_status, tune_get("prefill_test_expire"), tune_get("prefill_group")};
     if (!tune_get("prefill_force_simt")) {
         // "prefill_variant": 0 = one-CTA tensor-core kernel (default), 2 = CTA-pair kernel where its
         // shape limits allow
@@ -247,4 +247,59 @@ extern "C" int b2kv_prefill(const void* Q, const void* K, const void* V, void* O
         if (rc != B2KV_ERR_UNSUPPORTED) return rc;
     }
     return prefill_simt(p, D, dtype, stream);
+}
+
+namespace b2kv {
+// append.cu: rows [b * src_rows_per_seq + src_first + i], i < n_rows, of k_rows / v_rows to position first_pos + i of
+// sequence b through the block table.
+int append_rows_paged_from(const void* k_rows, const void* v_rows, void* k_pool, void* v_pool, const int32_t* block_table,
+                           int max_blocks, int block_size, int n_blocks, int B, int n_rows, int first_pos,
+                           int src_rows_per_seq, int src_first, int H, int D, int64_t stride_blk, int64_t stride_t,
+                           int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
+}  // namespace b2kv
+
+extern "C" int b2kv_prefill_paged(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_pool,
+                                  void* v_pool, const int32_t* block_table, int max_blocks, int block_size, int n_blocks,
+                                  int64_t stride_blk, int64_t stride_t, int64_t stride_h, int B, int N, int H, int D,
+                                  int dtype, int32_t* dev_status, void* stream) {
+    const int es = elt_bytes(dtype);
+    if (es == 0) return B2KV_ERR_UNSUPPORTED;
+    if (!Q || !K || !V || !O || !k_pool || !v_pool || !block_table) return B2KV_ERR_BAD_ARG;
+    if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || max_blocks <= 0 || block_size <= 0 || n_blocks <= 0) return B2KV_ERR_BAD_ARG;
+    if (static_cast<long long>(max_blocks) * block_size < N) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O) || !aligned16(k_pool) || !aligned16(v_pool))
+        return B2KV_ERR_ALIGN;
+    if ((D * es) % 16 != 0) return B2KV_ERR_UNSUPPORTED;
+    if (!stride_ok(stride_blk, es) || !stride_ok(stride_t, es) || !stride_ok(stride_h, es)) return B2KV_ERR_ALIGN;
+    PrefillParams p{Q, K, V, O, L, M, nullptr, nullptr, stride_blk, stride_t, stride_h, B, N, H,
+                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), nullptr, 0, 0, 0, 0, 0,
+                    dev_status, tune_get("prefill_test_expire"), tune_get("prefill_group")};
+    // The tensor-core kernel stores the whole blocks of the prompt itself, straight from its K / V rings, when a
+    // block is a whole number of 1 KB swizzle atoms (8 rows) and blocks tile its 128-row K / V tiles.
+    const bool tiles = block_size % 8 == 0 && (128 % block_size == 0 || block_size % 128 == 0);
+    int whole = 0;  // tokens that the attention kernel has written
+    if (!tune_get("prefill_force_simt") && !tune_get("prefill_unfused_paged") && tiles) {
+        PrefillParams pp = p;
+        pp.k_cache = k_pool;
+        pp.v_cache = v_pool;
+        pp.block_table = block_table;
+        pp.max_blocks = max_blocks;
+        pp.block_size = block_size;
+        pp.n_blocks = n_blocks;
+        pp.rows_per_store = block_size < 128 ? block_size : 128;
+        pp.n_whole = N / block_size * block_size;
+        const int rc = prefill_tensor_core(pp, D, dtype, stream);
+        if (rc == B2KV_OK) whole = pp.n_whole;
+        else if (rc != B2KV_ERR_UNSUPPORTED) return rc;
+    }
+    if (whole == 0) {
+        int rc = B2KV_ERR_UNSUPPORTED;
+        if (!tune_get("prefill_force_simt")) rc = prefill_tensor_core(p, D, dtype, stream);
+        if (rc == B2KV_ERR_UNSUPPORTED) rc = prefill_simt(p, D, dtype, stream);
+        if (rc != B2KV_OK) return rc;
+    }
+    if (whole == N) return B2KV_OK;
+    // what the attention kernel did not write (a last, partly filled block; or everything): a copy kernel behind it
+    return append_rows_paged_from(K, V, k_pool, v_pool, block_table, max_blocks, block_size, n_blocks, B, N - whole, whole,
+                                  N, whole, H, D, stride_blk, stride_t, stride_h, dtype, dev_status, stream);
 }

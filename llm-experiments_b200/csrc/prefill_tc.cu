@@ -8,7 +8,8 @@
 //     every K/V tile; 128-key K/V tiles up to the diagonal (A stops one tile before B);
 //   * warp 8 issues TMA tiled loads (cp.async.bulk.tensor, 128-byte swizzle) of Q, K and V tiles
 //     into shared memory rings that complete on mbarriers, and at the end TMA-stores the two
-//     diagonal K / V tiles (the CTA's own rows) from the ring into the KV cache;
+//     diagonal K / V tiles (the CTA's own rows) from the ring into the KV cache (a paged cache gets
+//     one store per whole block, at the block its table names);
 //   * warp 9 issues the MMAs from one thread: S_X = Q_X K^T (both operands K-major in shared memory)
 //     into the S buffer of tile X in TMEM, and O_X += P_X V with P_X read from TMEM (it overwrites
 //     S_X) and V as an MN-major shared-memory operand.  The order PV_A(j), QK_A(j+1), PV_B(j),
@@ -145,21 +146,40 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // the rings.  Once the MMAs that read a tile have completed (its "empty" barrier), store
             // it to the cache.  Rows past the sequence end are clipped by the tensor map.
             if (ok && p.k_cache != nullptr) {
+                // One tile of one ring to the cache: a contiguous cache takes it as one box per 64-column half; a
+                // paged cache takes every whole block of it as a box of its own, at the block the table names
+                // (rows past the prompt's last whole block are left to the copy kernel that follows).
+                auto store_tile = [&](const CUtensorMap* map, const uint8_t* tile, int t) {
+                    if (p.block_table == nullptr) {
+#pragma unroll
+                        for (int hf = 0; hf < kHalves; ++hf)
+                            tma_store_4d(map, tile + hf * kHalfTileBytes, hf * 64, t * kBlockN, h, b);
+                        return;
+                    }
+                    for (int r0 = 0; r0 < kBlockN; r0 += p.rows_per_store) {
+                        const int tok = t * kBlockN + r0;
+                        if (tok + p.rows_per_store > p.n_whole) break;
+                        const int blk = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+                        if (blk < 0 || blk >= p.n_blocks) {
+                            report_status(p.dev_status, B2KV_DEV_BAD_BLOCK);  // skipped: nothing is written outside the pool
+                            continue;
+                        }
+#pragma unroll
+                        for (int hf = 0; hf < kHalves; ++hf)
+                            tma_store_4d(map, tile + hf * kHalfTileBytes + r0 * 128, hf * 64, tok % p.block_size, h, blk);
+                    }
+                };
                 for (int t = qa; t < n_max && ok; ++t) {
                     const int st = t % kStages;
                     ok = mbar_wait(&sm.k_empty[st], (t / kStages) & 1);
                     if (!ok) break;
-#pragma unroll
-                    for (int hf = 0; hf < kHalves; ++hf)
-                        tma_store_4d(&tm_kc, sm.k[st] + hf * kHalfTileBytes, hf * 64, t * kBlockN, h, b);
+                    store_tile(&tm_kc, sm.k[st], t);
                 }
                 for (int t = qa; t < n_max && ok; ++t) {
                     const int st = t % kStages;
                     ok = mbar_wait(&sm.v_empty[st], (t / kStages) & 1);
                     if (!ok) break;
-#pragma unroll
-                    for (int hf = 0; hf < kHalves; ++hf)
-                        tma_store_4d(&tm_vc, sm.v[st] + hf * kHalfTileBytes, hf * 64, t * kBlockN, h, b);
+                    store_tile(&tm_vc, sm.v[st], t);
                 }
                 tma_store_commit();
                 tma_store_wait();
@@ -420,7 +440,15 @@ static int launch_prefill_tc(const PrefillParams& p_in, int dtype, void* stream)
     if (!tc::make_map(&tq, p.Q, p.B, p.N, E) || !tc::make_map(&tk, p.K, p.B, p.N, E) ||
         !tc::make_map(&tv, p.V, p.B, p.N, E))
         return B2KV_ERR_UNSUPPORTED;  // no tensor-map encoder in this driver: the SIMT kernel takes over
-    if (p.k_cache != nullptr) {
+    if (p.k_cache != nullptr && p.block_table != nullptr) {
+        // block pools as (d, token in block, head, block); one store moves rows_per_store rows of 64 columns
+        if (p.stride_t < D || p.stride_h <= 0 || p.stride_b <= 0) return B2KV_ERR_UNSUPPORTED;
+        if (!make_cache_tensor_map(&tkc, p.k_cache, dtype, D, p.block_size, p.H, p.n_blocks, p.stride_b, p.stride_t,
+                                   p.stride_h, 64, p.rows_per_store, CU_TENSOR_MAP_SWIZZLE_128B) ||
+            !make_cache_tensor_map(&tvc, p.v_cache, dtype, D, p.block_size, p.H, p.n_blocks, p.stride_b, p.stride_t,
+                                   p.stride_h, 64, p.rows_per_store, CU_TENSOR_MAP_SWIZZLE_128B))
+            return B2KV_ERR_UNSUPPORTED;
+    } else if (p.k_cache != nullptr) {
         // a cache whose strides a tensor map cannot express goes to the SIMT kernel
         if (p.stride_t < D || p.stride_h <= 0 || p.stride_b <= 0) return B2KV_ERR_UNSUPPORTED;
         // cut to the first N tokens, so that a store of a partly filled tile leaves the rows past the

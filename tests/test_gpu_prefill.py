@@ -124,13 +124,19 @@ def test_prefill_cta_pair_kernel_vs_oracle_and_one_cta_kernel(pkg, ctx, B, N, H,
         assert float(kview[:, N:].float().abs().sum()) == 0.0
 
 
-@pytest.mark.parametrize("dtype,D,N", [(torch.bfloat16, 128, 200), (torch.float32, 64, 77), (torch.bfloat16, 128, 256)])
-def test_prefill_into_a_paged_cache_bit_exact_then_decode_continues(pkg, ctx, dtype, D, N):
+@pytest.mark.parametrize("dtype,D,N,bs", [(torch.bfloat16, 128, 200, 16), (torch.float32, 64, 77, 16),
+                                          (torch.bfloat16, 128, 256, 16), (torch.bfloat16, 128, 300, 8),
+                                          (torch.bfloat16, 64, 200, 64), (torch.bfloat16, 128, 200, 128),
+                                          (torch.bfloat16, 128, 300, 256), (torch.bfloat16, 128, 200, 24),
+                                          (torch.bfloat16, 128, 260, 32)])
+def test_prefill_into_a_paged_cache_bit_exact_then_decode_continues(pkg, ctx, dtype, D, N, bs):
     """flash_attention with a paged cache: the prompt's K / V rows land in the blocks that a permuted block
     table names (bit-exact, nothing else in the pool touched), and decoding the last prompt token over the
-    pool reproduces the prefill's last row."""
+    pool reproduces the prefill's last row.  Block sizes that tile the kernel's 128-row K / V tiles are stored by
+    the tensor-core kernel itself (whole blocks; a partly filled last block by the copy kernel), the others
+    (24 here, and every fp32 case) by the copy kernel alone."""
     gpu = pkg.gpu
-    B, H, T_max, bs = 2, 3, 320, 16
+    B, H, T_max = 2, 3, 320
     E = H * D
     Q = U.randn((B, N, E), dtype, ctx.device, 31)
     K = U.randn((B, N, E), dtype, ctx.device, 32)
