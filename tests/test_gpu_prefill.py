@@ -141,7 +141,7 @@ def test_prefill_into_a_paged_cache_bit_exact_then_decode_continues(pkg, ctx, dt
     Q = U.randn((B, N, E), dtype, ctx.device, 31)
     K = U.randn((B, N, E), dtype, ctx.device, 32)
     V = U.randn((B, N, E), dtype, ctx.device, 33)
-    n_blocks = 64
+    n_blocks = max(64, B * ((T_max + bs - 1) // bs) + 7)
     cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H, head_dim=D,
                                                        dtype=dtype, block_size=bs, n_blocks=n_blocks))
     max_blocks = cache.block_table.shape[1]
