@@ -230,6 +230,21 @@ int b2kv_prefill(const void* Q, const void* K, const void* V, void* O, float* L,
                  int D, int dtype, int32_t* dev_status, void* stream);
 
 /*
+ * b2kv_prefill with a scratch buffer, which lets fp32 prompts (the reference's storage type) of head_dim 128 or 64 run
+ * on the tensor cores as well: Q, K and V are split into two bfloat16 halves each (x = hi + lo, 16 mantissa bits kept)
+ * in the scratch, every product becomes three MMAs into fp32 accumulators (the dropped lo * lo term is below 2^-16
+ * relative), softmax and outputs stay fp32; results agree with the fp32 oracle within rtol 1e-4 and atol 3e-5
+ * on outputs of order one (the SIMT kernel, which b2kv_prefill takes for fp32, holds atol 1e-5).  b2kv_prefill_workspace_bytes gives the scratch size, 0 where scratch buys nothing (bf16
+ * prompts, other head_dims, prompts shorter than 128 tokens): the call then is b2kv_prefill.  The scratch needs no
+ * initialisation and carries nothing between calls.  With a cache the K / V rows are written by a copy kernel behind the
+ * attention.
+ */
+size_t b2kv_prefill_workspace_bytes(int B, int N, int H, int D, int dtype);
+int b2kv_prefill_ws(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache, void* v_cache,
+                    int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B, int N, int H, int D, int dtype,
+                    void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream);
+
+/*
  * b2kv_prefill into a PAGED cache (no counterpart in the reference, whose cache is contiguous): the prompt's K / V
  * rows 0..N-1 of sequence b go to the pool blocks that block_table[b, :] names, addressed as in b2kv_append_paged.
  * On the tensor-core path (bf16, D == 128 or 64) the attention kernel stores every whole block itself from its
@@ -332,7 +347,8 @@ int b2kv_matmul(const void* a, const void* w, const void* bias, const void* resi
  * another thread is inside a b2kv call): sets an integer knob by name ("decode_variant",
  * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,
- * N a multiple of 256, "prefill_unfused_paged": 1 = b2kv_prefill_paged always
+ * N a multiple of 256, "prefill_f32_simt": 1 = b2kv_prefill_ws never takes the
+ * split-bfloat16 tensor-core kernel, "prefill_unfused_paged": 1 = b2kv_prefill_paged always
  * fills the pool with the copy kernel, "prefill_test_expire": 1 = test hook, the softmax warps of the one-CTA tensor-core prefill
  * behave as if their first bounded wait had run out (the launch then ends after about two seconds with
  * B2KV_DEV_WAIT_TIMEOUT in dev_status), "matmul_splits": ranges of input features per tile in b2kv_matmul_rows,

@@ -56,6 +56,9 @@ SIGNATURES = {
     "b2kv_merge_partials": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "b2kv_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "b2kv_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "b2kv_prefill_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _vp, _sz,
+                             _vp, _vp]),
     "b2kv_prefill_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i,
                                 _vp, _vp]),
     "b2kv_layernorm": (_i, [_vp, _vp, _vp, _vp, _i64, _i, ctypes.c_float, _vp]),

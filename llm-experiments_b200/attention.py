@@ -12,6 +12,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import torch
+
 from . import _native
 from .batch import batch_op_begin, dev_status_ptr, reference_op, validate_buffer_shape_1d, validate_buffer_shape_2d
 from .kv_cache import cache_strides, dtype_code
@@ -77,9 +79,16 @@ def flash_attention(ctx: GPUContext, Q: GPUBuffer2D, K: GPUBuffer2D, V: GPUBuffe
                                             batch_size, seq_len, n_heads, head_dim, dtype_code(dtype),
                                             dev_status_ptr(ctx), stream)
     else:
-        rc = _native.lib.b2kv_prefill(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(), O.buffer.data_ptr(),
-                                      *lm, kc, vc, s0, st, sh, t_max, batch_size, seq_len, n_heads, head_dim,
-                                      dtype_code(dtype), dev_status_ptr(ctx), stream)
+        # fp32 prompts of head_dim 128 / 64 run on the tensor cores when given scratch for their bfloat16 halves
+        ws_bytes = _native.lib.b2kv_prefill_workspace_bytes(batch_size, seq_len, n_heads, head_dim, dtype_code(dtype))
+        ws = None
+        if ws_bytes:
+            if ctx.prefill_workspace is None or ctx.prefill_workspace.numel() < ws_bytes:
+                ctx.prefill_workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=ctx.device)
+            ws = ctx.prefill_workspace.data_ptr()
+        rc = _native.lib.b2kv_prefill_ws(Q.buffer.data_ptr(), K.buffer.data_ptr(), V.buffer.data_ptr(), O.buffer.data_ptr(),
+                                         *lm, kc, vc, s0, st, sh, t_max, batch_size, seq_len, n_heads, head_dim,
+                                         dtype_code(dtype), ws, ws_bytes, dev_status_ptr(ctx), stream)
     _native.check(rc)
     if cache is not None:
         cache.current_len = seq_len

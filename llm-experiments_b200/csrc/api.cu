@@ -28,6 +28,7 @@ static Knob g_knobs[] = {
     {"decode_l2_keep", 0},  // 1 = K/V bulk copies use the default L2 policy instead of evict-first
     {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
     {"prefill_variant", 0},
+    {"prefill_f32_simt", 0},  // 1 = fp32 prompts never take the split-bfloat16 tensor-core kernel
     {"prefill_unfused_paged", 0},  // 1 = a paged cache is always filled by the copy kernel behind the attention
     {"prefill_test_expire", 0},  // test hook: 1 = the softmax warps of the one-CTA tensor-core prefill give up at once
     {"prefill_group", 0},  // one-CTA tensor-core prefill: (sequence, head) pairs per launch group; 0 = by size, -1 = all

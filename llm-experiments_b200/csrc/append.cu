@@ -148,6 +148,28 @@ static int launch_gather(const void* cache, void* out, RowMap m, int B, int H, i
     return B2KV_OK;
 }
 
+// Rows [b * n_rows + i] of k_rows / v_rows to position i of sequence b of a contiguous cache (a whole prompt).
+int append_rows_contiguous(const void* k_rows, const void* v_rows, void* k_cache, void* v_cache, int B, int n_rows, int H,
+                           int D, int T_max, int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype,
+                           int32_t* dev_status, void* stream) {
+    int rc = check_common(B, H, D, dtype, stride_b, stride_t, stride_h);
+    if (rc != B2KV_OK) return rc;
+    if (!k_rows || !v_rows || !k_cache || !v_cache || n_rows <= 0 || n_rows > T_max) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(k_rows) || !aligned16(v_rows) || !aligned16(k_cache) || !aligned16(v_cache)) return B2KV_ERR_ALIGN;
+    if (B > 65535) return B2KV_ERR_UNSUPPORTED;
+    RowMap m{nullptr, 0, nullptr, 0, 0, 0, stride_b, stride_t, stride_h, T_max, dev_status};
+    const int es = elt_bytes(dtype);
+    const int chunks = H * D * es / 16;
+    const int shift = es == 4 ? 2 : 3;
+    int threads = (chunks + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    append_rows_kernel<<<dim3(n_rows, B), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(k_rows), static_cast<const uint4*>(v_rows), static_cast<uint4*>(k_cache),
+        static_cast<uint4*>(v_cache), m, n_rows, 0, 0, H, D, chunks, shift);
+    B2KV_CUDA_TRY(cudaGetLastError());
+    return B2KV_OK;
+}
+
 int append_rows_paged_from(const void* k_rows, const void* v_rows, void* k_pool, void* v_pool, const int32_t* block_table,
                            int max_blocks, int block_size, int n_blocks, int B, int n_rows, int first_pos,
                            int src_rows_per_seq, int src_first, int H, int D, int64_t stride_blk, int64_t stride_t,

@@ -31,6 +31,11 @@ struct PrefillParams {
 int prefill_simt(const PrefillParams& p, int D, int dtype, void* stream);
 // Tensor-core kernel: returns B2KV_ERR_UNSUPPORTED when the shape is not one it takes.
 int prefill_tensor_core(const PrefillParams& p, int D, int dtype, void* stream);
+// Tensor-core kernel for fp32 prompts (head_dim 128 or 64): operands split into bfloat16 halves in `scratch`
+// (prefill_f32_scratch_bytes), three MMAs per product.  Writes no cache rows.  B2KV_ERR_UNSUPPORTED when the shape or
+// the scratch does not fit.
+size_t prefill_f32_scratch_bytes(int B, int N, int H, int D);
+int prefill_tensor_core_f32(const PrefillParams& p, int D, void* scratch, size_t scratch_bytes, void* stream);
 // Tensor-core kernel on CTA pairs (bf16, head_dim 128, N a multiple of 256): same contract.
 int prefill_tensor_core_pair(const PrefillParams& p, int D, int dtype, void* stream);
 

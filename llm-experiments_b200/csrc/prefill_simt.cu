@@ -258,6 +258,49 @@ int append_rows_paged_from(const void* k_rows, const void* v_rows, void* k_pool,
                            int64_t stride_h, int dtype, int32_t* dev_status, void* stream);
 }  // namespace b2kv
 
+namespace b2kv {
+int append_rows_contiguous(const void* k_rows, const void* v_rows, void* k_cache, void* v_cache, int B, int n_rows, int H,
+                           int D, int T_max, int64_t stride_b, int64_t stride_t, int64_t stride_h, int dtype,
+                           int32_t* dev_status, void* stream);
+}  // namespace b2kv
+
+extern "C" size_t b2kv_prefill_workspace_bytes(int B, int N, int H, int D, int dtype) {
+    // scratch only buys something for fp32 prompts that the tensor-core kernel takes, and only from a row block on
+    if (dtype != B2KV_DTYPE_F32 || B <= 0 || N < 128 || H <= 0) return 0;
+    return prefill_f32_scratch_bytes(B, N, H, D);
+}
+
+extern "C" int b2kv_prefill_ws(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_cache,
+                               void* v_cache, int64_t stride_b, int64_t stride_t, int64_t stride_h, int T_max, int B,
+                               int N, int H, int D, int dtype, void* workspace, size_t workspace_bytes,
+                               int32_t* dev_status, void* stream) {
+    const size_t need = b2kv_prefill_workspace_bytes(B, N, H, D, dtype);
+    if (need == 0 || workspace == nullptr || workspace_bytes < need || tune_get("prefill_force_simt") ||
+        tune_get("prefill_f32_simt"))
+        return b2kv_prefill(Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, T_max, B, N, H, D, dtype,
+                            dev_status, stream);
+    // the same argument checks as b2kv_prefill, then the tensor-core kernel and, for a cache, the copy kernel
+    if (!Q || !K || !V || !O) return B2KV_ERR_BAD_ARG;
+    if ((k_cache == nullptr) != (v_cache == nullptr)) return B2KV_ERR_BAD_ARG;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O) || !aligned16(k_cache) || !aligned16(v_cache) ||
+        !aligned16(workspace))
+        return B2KV_ERR_ALIGN;
+    if (k_cache) {
+        if (N > T_max) return B2KV_ERR_BAD_ARG;
+        if (!stride_ok(stride_b, 4) || !stride_ok(stride_t, 4) || !stride_ok(stride_h, 4)) return B2KV_ERR_ALIGN;
+    }
+    PrefillParams p{Q, K, V, O, L, M, nullptr, nullptr, 0, 0, 0, B, N, H,
+                    static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), nullptr, 0, 0, 0, 0, 0,
+                    dev_status, 0, 0};
+    int rc = prefill_tensor_core_f32(p, D, workspace, workspace_bytes, stream);
+    if (rc == B2KV_ERR_UNSUPPORTED)
+        return b2kv_prefill(Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, T_max, B, N, H, D, dtype,
+                            dev_status, stream);
+    if (rc != B2KV_OK || k_cache == nullptr) return rc;
+    return append_rows_contiguous(K, V, k_cache, v_cache, B, N, H, D, T_max, stride_b, stride_t, stride_h, dtype,
+                                  dev_status, stream);
+}
+
 extern "C" int b2kv_prefill_paged(const void* Q, const void* K, const void* V, void* O, float* L, float* M, void* k_pool,
                                   void* v_pool, const int32_t* block_table, int max_blocks, int block_size, int n_blocks,
                                   int64_t stride_blk, int64_t stride_t, int64_t stride_h, int B, int N, int H, int D,

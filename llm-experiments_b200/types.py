@@ -115,6 +115,7 @@ class GPUContext:
     reduction_workspace: Optional[GPUBuffer1D] = None
     dev_status: Optional[torch.Tensor] = None  # int32[1], written by kernels that detect a bad index
     perf_monitor: Optional[PerfMonitor] = None  # filled by batches opened with enable_profiling
+    prefill_workspace: Optional[torch.Tensor] = None  # scratch of flash_attention for fp32 prompts, grown on demand
 
 
 @dataclass

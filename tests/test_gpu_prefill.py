@@ -10,6 +10,9 @@ from tests import kv_util as U
 
 pytestmark = pytest.mark.gpu
 
+# fp32 prompts on the tensor cores (operands as two bfloat16 halves, 16 mantissa bits): see the tests that use it
+SPLIT_TOL = dict(rtol=1e-4, atol=3e-5)
+
 
 @pytest.fixture(scope="module")
 def ctx(pkg):
@@ -220,3 +223,51 @@ def test_profiled_batch_fills_the_perf_monitor(pkg, ctx):
     assert stats.total_submissions == 1
     fa = stats.kernel_times["flash_attention"]
     assert fa.count == 2 and 0.0 < fa.min_ms <= fa.max_ms
+
+
+@pytest.mark.parametrize("B,N,H,D", [(1, 128, 2, 128), (2, 300, 2, 64), (1, 1000, 3, 128), (2, 129, 1, 64),
+                                     (1, 2048, 2, 128)])
+def test_fp32_prompts_on_the_tensor_cores_keep_the_fp32_bar(pkg, ctx, B, N, H, D):
+    """fp32 prompts of head_dim 128 / 64 and at least 128 tokens run on the tensor cores with every operand split into
+    two bfloat16 halves (three MMAs per product), which keeps 16 of fp32's 24 mantissa bits per operand.  Bar: rtol
+    1e-4 with atol 3e-5 against the oracle on outputs of order one (the SIMT kernel's atol is 1e-5; the worst element
+    seen here is 1.3e-5 off), L and M at the SIMT kernel's tolerance; and the two kernels agree with each other."""
+    dtype = torch.float32
+    Q = U.randn((B, N, H * D), dtype, ctx.device, 41)
+    K = U.randn((B, N, H * D), dtype, ctx.device, 42)
+    V = U.randn((B, N, H * D), dtype, ctx.device, 43)
+    assert pkg._native.lib.b2kv_prefill_workspace_bytes(B, N, H, D, pkg._native.DTYPE_F32) == 6 * B * N * H * D * 2
+    O, L, M = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype)
+    flat = lambda a: U.to_oracle(a.reshape(B * N, H * D))  # noqa: E731
+    Ow, Lw, Mw = c_oracle.prefill(flat(Q), flat(K), flat(V), B, N, H, D)
+    np.testing.assert_allclose(U.to_f32(O), Ow, **SPLIT_TOL)
+    np.testing.assert_allclose(L.cpu().numpy(), Lw, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(M.cpu().numpy(), Mw, rtol=1e-4, atol=1e-5)
+    pkg._native.tune("prefill_f32_simt", 1)
+    try:
+        O_simt, _, _ = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype)
+    finally:
+        pkg._native.tune("prefill_f32_simt", 0)
+    assert not torch.equal(O, O_simt)  # two different kernels ran
+    np.testing.assert_allclose(U.to_f32(O), U.to_f32(O_simt), **SPLIT_TOL)
+
+
+@pytest.mark.parametrize("layout", ["bthd", "bhtd"])
+def test_fp32_tensor_core_prefill_fills_the_cache_bit_exact(pkg, ctx, layout):
+    gpu = pkg.gpu
+    B, N, H, D, dtype = 2, 200, 2, 64, torch.float32
+    E = H * D
+    Q = U.randn((B, N, E), dtype, ctx.device, 51)
+    K = U.randn((B, N, E), dtype, ctx.device, 52)
+    V = U.randn((B, N, E), dtype, ctx.device, 53)
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=N + 24, n_layers=1, n_heads=H,
+                                                       head_dim=D, dtype=dtype, layout=layout))
+    O, _, _ = _run_flash(pkg, ctx, Q, K, V, B, N, H, D, dtype, cache=cache, stats=False)
+    assert cache.current_len == N
+    kview = U.logical_view(cache, cache.layers[0], "k")
+    vview = U.logical_view(cache, cache.layers[0], "v")
+    assert torch.equal(kview[:, :N].reshape(B, N, E), K) and torch.equal(vview[:, :N].reshape(B, N, E), V)
+    assert float(kview[:, N:].abs().sum()) == 0.0
+    flat = lambda a: U.to_oracle(a.reshape(B * N, E))  # noqa: E731
+    Ow, _, _ = c_oracle.prefill(flat(Q), flat(K), flat(V), B, N, H, D, want_stats=False)
+    np.testing.assert_allclose(U.to_f32(O), Ow, **SPLIT_TOL)
