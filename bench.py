@@ -88,6 +88,9 @@ WORKLOADS = {
     "model_step": dict(kind="model_step", B=64, H=32, D=128, lo=512, hi=8192, layers=4, vocab=32768,
                        desc="one cached decode step of a 4-layer bf16 decoder (E=4096, H=32, vocab 32768): embedding, "
                             "4 decoder layers, final layernorm, logits, argmax; B=64, len~U[512,8192] seed 0"),
+    "model_step_small": dict(kind="model_step", B=8, H=32, D=128, lo=128, hi=1024, layers=4, vocab=32768,
+                             desc="the same 4-layer decoder at B=8 with short contexts, len~U[128,1024] seed 0: a step is "
+                                  "bound by its 36 launches, so it is also timed as one replayed CUDA graph"),
 }
 SLACK = 1024  # rows of head-room above the longest sequence for the appended tokens
 
@@ -980,6 +983,21 @@ def run_model_step(h: Harness, w):
         gpu.gpu_buffer_1d_read(ctx, next_b, next_h)
 
     m_e2e = h.measure(step_e2e, warmup=1)
+
+    # the same step as one replayed CUDA graph (what a launch-bound step gains from it)
+    for c in state.caches:
+        gpu.kv_cache_set_lengths(c, lens)
+    graphed = model.GraphedDecodeStep(ctx, state)
+    graphed.token_ids.buffer.copy_(tokens)
+    graphed.capture()
+
+    def step_graph():
+        for c in state.caches:
+            c.seq_lens.copy_(lens_dev)
+            c.current_len = max_len
+        graphed.step()
+
+    m_graph = h.measure(step_graph)
     clocks = sampler.finish()
     status = int(ctx.dev_status.item()) if ctx.dev_status is not None else 0
     es = 2
@@ -999,6 +1017,8 @@ def run_model_step(h: Harness, w):
                 "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4},
         "gpu_launches": h.steps * h.repeats * launches, "gpu_launches_per_step": launches, "clocks": clocks,
         "dev_status": status,
+        "cuda_graph": {"value": world * B / (m_graph["ms"] * 1e-3), "unit": "tokens/s", **spread(m_graph),
+                       "what": "the same step captured once and replayed (one graph launch per step)"},
         "roofline": {"bound": "hbm", "kernel": f"the step's {launches} kernels together", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": kind,
                      "algorithmic_bytes_per_launch": bytes_step, "kv_bytes": kv_bytes, "weight_bytes": weight_bytes,
@@ -1074,7 +1094,7 @@ def run_b200(args):
         "gpu_launches_per_step": head.get("gpu_launches_per_step"), "clocks": head["clocks"],
         "roofline": head["roofline"], "cpu_baseline": head.get("cpu_baseline"),
     }
-    for k in ("step_hbm_gbs", "dev_status"):
+    for k in ("step_hbm_gbs", "dev_status", "cuda_graph"):
         if k in head:
             line[k] = head[k]
     line.update(extra)

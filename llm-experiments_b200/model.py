@@ -201,6 +201,82 @@ def prefill(ctx: GPUContext, state: DecoderState, prompt_ids: GPUBuffer1D, seq_l
     _head(ctx, state, state.last, next_ids)
 
 
+class GraphedDecodeStep:
+    """``decode_step`` captured once into a CUDA graph and replayed: one graph launch per generated token instead
+    of ``launches_per_decode_step`` kernel launches issued from Python, which is what bounds small batches and
+    short contexts (a step of a few hundred microseconds on the GPU against about ten microseconds of host work
+    per launch).  The reference records its operations into one command encoder per batch and submits them
+    together (simple-llm/src/gpu/gpu_ops.py:226-360); a replayed graph is the CUDA form of re-submitting that
+    encoder.
+
+    The state must keep its lengths on the device (``ragged=True``): the kernels of the captured step read the
+    positions and lengths from there, so the same graph serves every step.  The host-side ``current_len`` of the
+    caches, which sizes launches, is pinned to the cache capacity while capturing; ``step()`` advances it afterwards
+    like the eager call does.  ``token_ids`` and ``next_ids`` are fixed buffers: write the step's tokens into
+    ``token_ids`` (or pass ``feed_back=True`` to copy ``next_ids`` there on the device after every step).
+    """
+
+    def __init__(self, ctx: GPUContext, state: DecoderState, feed_back: bool = False):
+        if any(c.seq_lens is None for c in state.caches):
+            raise ValueError("a graphed decode step needs per-sequence lengths on the device (ragged=True)")
+        self.ctx, self.state, self.feed_back = ctx, state, feed_back
+        B = state.batch_size
+        self.token_ids = _b1(torch.zeros(B, dtype=torch.int32, device=ctx.device))
+        self.next_ids = _b1(torch.zeros(B, dtype=torch.int32, device=ctx.device))
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def _record(self) -> None:
+        ctx, state = self.ctx, self.state
+        batch_begin(ctx)
+        decode_step(ctx, state, self.token_ids, self.next_ids)
+        batch_commit(ctx)
+        if self.feed_back:
+            self.token_ids.buffer.copy_(self.next_ids.buffer)
+
+    def capture(self) -> None:
+        """Runs one eager step on a side stream (first-use set-up of every kernel, scratch allocations), restores the
+        lengths it advanced, then captures the step.  Call it when at least one more token fits every cache."""
+        ctx, state = self.ctx, self.state
+        if ctx.config.check_device_status:
+            raise ValueError("check_device_status synchronises in batch_commit, which a graph capture cannot hold")
+        caches = state.caches
+        cap = caches[0].max_seq_len
+        keep_len = [c.current_len for c in caches]
+        if max(keep_len) >= cap:
+            raise ValueError(f"Cache is full: current_len={max(keep_len)}, max_seq_len={cap}")
+        keep_dev = [c.seq_lens.clone() for c in caches]
+        keep_tok = self.token_ids.buffer.clone()
+        side = torch.cuda.Stream(device=ctx.device)
+        side.wait_stream(torch.cuda.current_stream(ctx.device))
+        with torch.cuda.stream(side):
+            self._record()  # warm-up: nothing allocates or configures a kernel inside the capture
+            for c, n, dev in zip(caches, keep_len, keep_dev):
+                c.current_len = cap - 1  # launches sized for the longest sequence the cache can hold
+                c.seq_lens.copy_(dev)
+            self.token_ids.buffer.copy_(keep_tok)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                self._record()
+            for c, dev in zip(caches, keep_dev):
+                c.seq_lens.copy_(dev)  # (the capture itself ran nothing)
+            self.token_ids.buffer.copy_(keep_tok)
+        torch.cuda.current_stream(ctx.device).wait_stream(side)
+        for c, n in zip(caches, keep_len):
+            c.current_len = n
+        self.graph = graph
+
+    def step(self) -> None:
+        """One decode step: replays the graph on torch's current stream and advances the host-side lengths."""
+        if self.graph is None:
+            self.capture()
+        caches = self.state.caches
+        if caches[0].current_len >= caches[0].max_seq_len:
+            raise ValueError(f"Cache is full: current_len={caches[0].current_len}, max_seq_len={caches[0].max_seq_len}")
+        self.graph.replay()
+        for c in caches:
+            c.current_len += 1
+
+
 class CachedDecoder:
     """Batch-of-one adapter with the interface ``generate_text`` drives: ``cache``, ``context``,
     ``prefill(tokens) -> logits [1, vocab]`` and ``decode_step(token) -> logits [1, vocab]`` (float32)."""

@@ -105,3 +105,70 @@ def test_generate_text_drives_the_cached_decoder(pkg):
     assert greedy == by_hand
     sampled = generate.generate_text(dec, prompt, max_tokens=6, temperature=0.8, top_k=20, top_p=0.9, seed=42)
     assert len(sampled) == 15 and all(0 <= t < 512 for t in sampled)
+
+
+def test_graphed_decode_step_equals_the_eager_step(pkg):
+    """decode_step captured into a CUDA graph and replayed gives the same logits and cache rows as the eager step,
+    step after step, on ragged lengths (same tokens fed to both); the host-side lengths advance alike.  The two are
+    not bit-identical: the captured attention launch is sized for the cache's capacity, so its split-K cuts fall
+    elsewhere and the fp32 partial sums are added in another order."""
+    from llm_experiments_b200 import model
+
+    gpu = pkg.gpu
+    ctx = gpu.context_create(0)
+    cfg = model.DecoderConfig(vocab_size=512, context_size=96, embedding_dim=256, n_heads=2, n_layers=2)
+    weights = model.weights_from_numpy(ctx, cfg, _params(cfg, model, seed=9))
+    B, N, steps = 3, 32, 6
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab_size, size=B * N).astype(np.int32)
+    lens = [32, 7, 19]  # after the prompt pass the sequences are cut back to ragged lengths
+    fed = [torch.from_numpy(np.random.default_rng(10 + i).integers(0, cfg.vocab_size, size=B).astype(np.int32))
+           for i in range(steps)]
+    runs = {}
+    for mode in ("eager", "graph", "graph_feed_back"):
+        state = model.decoder_state_create(ctx, cfg, weights, batch_size=B, ragged=True)
+        ids = gpu.gpu_buffer_1d_create(ctx, B * N, torch.from_numpy(prompt), dtype=torch.int32)
+        nxt = gpu.gpu_buffer_1d_create(ctx, B, dtype=torch.int32)
+        gpu.batch_begin(ctx)
+        model.prefill(ctx, state, ids, N, nxt)
+        gpu.batch_commit(ctx)
+        for c in state.caches:
+            gpu.kv_cache_set_lengths(c, lens)
+        tokens, logits = [], []
+        if mode == "eager":
+            tok = gpu.gpu_buffer_1d_create(ctx, B, dtype=torch.int32)
+            for i in range(steps):
+                tok.buffer.copy_(fed[i])
+                gpu.batch_begin(ctx)
+                model.decode_step(ctx, state, tok, nxt)
+                gpu.batch_commit(ctx)
+                tokens.append(nxt.buffer.cpu().clone())
+                logits.append(state.logits.buffer.float().cpu().clone())
+        else:
+            graphed = model.GraphedDecodeStep(ctx, state, feed_back=(mode == "graph_feed_back"))
+            graphed.token_ids.buffer.copy_(fed[0])
+            graphed.capture()
+            assert [c.current_len for c in state.caches] == [max(lens)] * cfg.n_layers
+            assert state.caches[0].seq_lens.tolist() == lens  # the warm-up step was undone
+            assert torch.equal(graphed.token_ids.buffer.cpu(), fed[0])
+            for i in range(steps):
+                if mode == "graph":
+                    graphed.token_ids.buffer.copy_(fed[i])
+                graphed.step()
+                tokens.append(graphed.next_ids.buffer.cpu().clone())
+                logits.append(state.logits.buffer.float().cpu().clone())
+            if mode == "graph_feed_back":  # every step was fed the step before's choice, on the device
+                assert torch.equal(graphed.token_ids.buffer.cpu(), tokens[-1])
+        torch.cuda.synchronize()
+        runs[mode] = (tokens, logits, [c.current_len for c in state.caches], state.caches[0].seq_lens.tolist(),
+                      state.caches[-1].layers[0].k_cache.buffer.float().cpu().clone())
+    for a, b in zip(runs["eager"][1], runs["graph"][1]):
+        assert float((a - b).abs().max()) <= 2e-2
+    assert torch.equal(runs["graph_feed_back"][0][0], runs["graph"][0][0])  # the first step saw the same tokens
+    for mode in ("graph", "graph_feed_back"):
+        assert runs["eager"][2] == runs[mode][2] == [max(lens) + steps] * cfg.n_layers
+        assert runs["eager"][3] == runs[mode][3] == [n + steps for n in lens]
+    # cache rows within each sequence's length agree (rows past it may differ: the warm-up step wrote one there)
+    k_e = runs["eager"][4].view(B, cfg.n_heads, cfg.context_size, cfg.head_dim)
+    k_g = runs["graph"][4].view(B, cfg.n_heads, cfg.context_size, cfg.head_dim)
+    for b, n in enumerate(lens):
+        assert float((k_e[b, :, : n + steps] - k_g[b, :, : n + steps]).abs().max()) <= 2e-2
