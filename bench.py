@@ -1106,7 +1106,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--repeats", type=int, default=5, help="timed loops of --steps steps each; medians are reported")
+    ap.add_argument("--repeats", type=int, default=10, help="timed loops of --steps steps each; medians are reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS))
     ap.add_argument("--only", action="store_true", help="time the named workload alone, without the sub-records")
