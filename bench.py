@@ -85,6 +85,9 @@ WORKLOADS = {
                           desc="causal prefill cut to 2 sequences (for profiler captures)"),
     "prefill": dict(kind="prefill", B=8, H=32, D=128, N=4096,
                     desc="causal prefill: B=8 H=32 D=128 N=4096 bf16, fused with the K/V cache write"),
+    "prefill_f32": dict(kind="prefill", B=2, H=32, D=128, N=4096, f32=True,
+                        desc="causal prefill of fp32 prompts (the reference's storage type) on the tensor cores, operands split "
+                             "into bfloat16 halves: B=2 H=32 D=128 N=4096, fused with the K/V cache write"),
     "model_step": dict(kind="model_step", B=64, H=32, D=128, lo=512, hi=8192, layers=4, vocab=32768,
                        desc="one cached decode step of a 4-layer bf16 decoder (E=4096, H=32, vocab 32768): embedding, "
                             "4 decoder layers, final layernorm, logits, argmax; B=64, len~U[512,8192] seed 0"),
@@ -646,7 +649,9 @@ def run_prefill(h: Harness, w):
     rank, world, device = h.rank, h.world, h.device
     B, H, D, N = w["B"], w["H"], w["D"], w["N"]
     E = H * D
-    dtype = torch.bfloat16
+    f32 = bool(w.get("f32"))
+    dtype = torch.float32 if f32 else torch.bfloat16
+    es = 4 if f32 else 2
     gen = torch.Generator(device=device).manual_seed(2000 + rank)
     mk = lambda: torch.randn((B * N, E), generator=gen, device=device, dtype=torch.float32).to(dtype)  # noqa: E731
     Q, K, V = mk(), mk(), mk()
@@ -680,18 +685,23 @@ def run_prefill(h: Harness, w):
     flops = 4.0 * B * H * D * N * (N + 1) / 2
     _, sustained, burst, kind = measured_peaks()
     achieved = flops / (m_step["ms"] * 1e-3) / 1e12
-    traffic = B * PREFILL_DRAM_BYTES_PER_SEQUENCE if ((H, D, N) == (32, 128, 4096) and not h.tuned) else None
+    traffic = B * PREFILL_DRAM_BYTES_PER_SEQUENCE if ((H, D, N) == (32, 128, 4096) and not h.tuned and not f32) else None
     rec = {
         "metric": "prefill tokens/s", "value": world * B * N / (m_step["ms"] * 1e-3), "unit": "tokens/s",
         **spread(m_step), "steps": steps, "scaling": "weak",
-        "dtype": "bf16 operands, fp32 accumulate",
+        "dtype": ("fp32 storage, operands as two bf16 halves (three MMAs per product), fp32 accumulate" if f32
+                  else "bf16 operands, fp32 accumulate"),
         "config": {"workload": w["desc"], "batch_per_gpu": B, "global_batch": world * B,
-                   "l2": "Q/K/V/O/cache (1.6 GB per step) larger than L2, no flush",
+                   "l2": f"Q/K/V/O/cache ({6 * B * N * E * es / 1e9:.1f} GB per step) larger than L2, no flush",
                    "parallelism": f"batch-sharded x{world}, no collective"},
         "e2e": {"value": world * B * N / (m_e2e["ms"] * 1e-3), "unit": "tokens/s", **spread(m_e2e),
-                "h2d_bytes_per_step": 3 * B * N * E * 2, "d2h_bytes_per_step": B * N * E * 2},
-        "gpu_launches": steps * h.repeats, "gpu_launches_per_step": 1, "clocks": clocks, "dev_status": status,
-        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": achieved, "peak": sustained,
+                "h2d_bytes_per_step": 3 * B * N * E * es, "d2h_bytes_per_step": B * N * E * es},
+        "gpu_launches": steps * h.repeats * (5 if f32 else 1), "gpu_launches_per_step": 5 if f32 else 1, "clocks": clocks,
+        "dev_status": status,
+        "roofline": {"bound": "tensor",
+                     "kernel": ("prefill_tc_f32_kernel (+ 3 split_kernel, append_rows_kernel); flops counted once per "
+                                "fp32 product, the kernel issues three bf16 MMAs for each" if f32 else "prefill_tc_kernel"),
+                     "achieved": achieved, "peak": sustained,
                      "unit": "TFLOP/s", "frac": achieved / sustained, "frac_of_burst": achieved / burst,
                      "peak_kind": kind + " (sustained cuBLAS bf16; kernel timed in a loop)",
                      "algorithmic_flops_per_launch": flops, "traffic": traffic,
@@ -702,8 +712,11 @@ def run_prefill(h: Harness, w):
         from oracle import c_oracle
 
         hs = 4  # heads of one sequence timed on the CPU
-        sl = lambda X: np.ascontiguousarray(  # noqa: E731
-            X.reshape(B, N, H, D)[0, :, :hs, :].reshape(N, hs * D).cpu().view(torch.int16).numpy().view(np.uint16))
+        if f32:
+            sl = lambda X: np.ascontiguousarray(X.reshape(B, N, H, D)[0, :, :hs, :].reshape(N, hs * D).cpu().numpy())  # noqa: E731
+        else:
+            sl = lambda X: np.ascontiguousarray(  # noqa: E731
+                X.reshape(B, N, H, D)[0, :, :hs, :].reshape(N, hs * D).cpu().view(torch.int16).numpy().view(np.uint16))
         t0 = time.perf_counter()
         c_oracle.prefill(sl(Q), sl(K), sl(V), 1, N, hs, D, want_stats=False)
         dt = time.perf_counter() - t0

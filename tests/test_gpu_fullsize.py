@@ -175,3 +175,56 @@ def test_long_context_decode_full_size_sampled_oracle(pkg, ctx):
     vbuf.fill_(1.0)
     ones = _decode(pkg, ctx, cache, q)
     assert torch.allclose(ones.float(), torch.ones_like(ones, dtype=torch.float32), atol=1e-2)
+
+
+def test_prefill_full_size_into_a_paged_cache_and_fp32_on_the_tensor_cores(pkg, ctx):
+    """The prefill configuration (B=8, H=32, D=128, N=4096, bf16) into a paged cache of 16-token blocks: the tensor-core
+    kernel stores the blocks itself, the output is bit-identical to the run into a contiguous cache and the pool
+    gathers back to K and V bit-exactly.  Then the same shape cut to two sequences in fp32 (split-bfloat16 operands),
+    sampled against the oracle."""
+    gpu = pkg.gpu
+    B, H, D, N, bs = 8, 32, 128, 4096, 16
+    E = H * D
+    dtype = torch.bfloat16
+    Q = U.randn((B * N, E), dtype, ctx.device, 61)
+    K = U.randn((B * N, E), dtype, ctx.device, 62)
+    V = U.randn((B * N, E), dtype, ctx.device, 63)
+    outs = []
+    for paged in (False, True):
+        cfg = dict(batch_size=B, max_seq_len=N, n_layers=1, n_heads=H, head_dim=D, dtype=dtype)
+        cfg.update(dict(block_size=bs, n_blocks=B * N // bs + 11) if paged else dict(layout="bhtd"))
+        cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(**cfg))
+        if paged:
+            perm = torch.randperm(cache.n_blocks, generator=torch.Generator().manual_seed(3))[: B * N // bs]
+            cache.block_table.copy_(perm.to(torch.int32).reshape(B, N // bs).to(ctx.device))
+        O = torch.empty_like(Q)
+        gpu.batch_begin(ctx)
+        gpu.flash_attention(ctx, U.buf2d(pkg, ctx, Q), U.buf2d(pkg, ctx, K), U.buf2d(pkg, ctx, V), U.buf2d(pkg, ctx, O),
+                            None, None, B, N, H, D, cache=cache, layer_idx=0)
+        gpu.batch_commit(ctx)
+        outs.append(O)
+        if paged:
+            gpu.batch_begin(ctx)
+            for which, src in (("k", K), ("v", V)):
+                rows = gpu.kv_cache_gather(ctx, cache, 0, which, length=N)
+                assert torch.equal(rows.reshape(B * N, E), src)
+                del rows
+            gpu.batch_commit(ctx)
+        del cache
+    assert torch.equal(outs[0], outs[1])
+    del outs, Q, K, V
+    torch.cuda.empty_cache()
+    B2 = 2
+    Qf = U.randn((B2 * N, E), torch.float32, ctx.device, 64)
+    Kf = U.randn((B2 * N, E), torch.float32, ctx.device, 65)
+    Vf = U.randn((B2 * N, E), torch.float32, ctx.device, 66)
+    Of = torch.empty_like(Qf)
+    gpu.batch_begin(ctx)
+    gpu.flash_attention(ctx, U.buf2d(pkg, ctx, Qf), U.buf2d(pkg, ctx, Kf), U.buf2d(pkg, ctx, Vf), U.buf2d(pkg, ctx, Of),
+                        None, None, B2, N, H, D)
+    gpu.batch_commit(ctx)
+    torch.cuda.synchronize()
+    for b, h in [(0, 0), (1, 31)]:
+        sl = lambda X: U.to_oracle(X.reshape(B2, N, H, D)[b, :, h].contiguous())  # noqa: E731
+        Ow, _, _ = c_oracle.prefill(sl(Qf), sl(Kf), sl(Vf), 1, N, 1, D, want_stats=False)
+        np.testing.assert_allclose(Of.reshape(B2, N, H, D)[b, :, h].cpu().numpy(), Ow, rtol=1e-4, atol=3e-5)
