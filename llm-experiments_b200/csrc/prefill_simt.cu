@@ -291,7 +291,7 @@ extern "C" int b2kv_prefill_ws(const void* Q, const void* K, const void* V, void
     }
     PrefillParams p{Q, K, V, O, L, M, nullptr, nullptr, 0, 0, 0, B, N, H,
                     static_cast<float>(1.4426950408889634 / sqrt(static_cast<double>(D))), nullptr, 0, 0, 0, 0, 0,
-                    dev_status, 0, 0};
+                    dev_status, 0, tune_get("prefill_group")};
     int rc = prefill_tensor_core_f32(p, D, workspace, workspace_bytes, stream);
     if (rc == B2KV_ERR_UNSUPPORTED)
         return b2kv_prefill(Q, K, V, O, L, M, k_cache, v_cache, stride_b, stride_t, stride_h, T_max, B, N, H, D, dtype,

@@ -23,6 +23,8 @@
 // Tensor memory: S / P columns 0 - 127, O columns 128 - 255.  Every mbarrier wait is bounded.
 #include <math.h>
 
+#include <algorithm>
+
 #include "prefill.cuh"
 #include "tc_ptx.cuh"
 #include "tma_map.cuh"
@@ -83,11 +85,18 @@ prefill_tc_f32_kernel(const __grid_constant__ CUtensorMap tm_qh, const __grid_co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rb = (p.N + kTileM - 1) / kTileM;
-    // heaviest row blocks first; the row blocks of a (sequence, head) next to each other, so that they find its
-    // K / V halves in L2
+    // Launch order: groups of `group` (sequence, head) pairs whose K / V halves together fit a quarter of L2; inside a
+    // group the heaviest row blocks first.  The CTAs running together then share the K / V of few pairs, which stay
+    // in L2 (with all pairs interleaved the halves were re-read from HBM five times over).
     const int n_bh = p.H * p.B;
-    const int rb = n_rb - 1 - static_cast<int>(blockIdx.x) / n_bh;
-    const int bh = static_cast<int>(blockIdx.x) % n_bh;
+    const int group = (p.group > 0 && p.group < n_bh) ? p.group : n_bh;
+    const int per_group = group * n_rb;
+    const int gi = static_cast<int>(blockIdx.x) / per_group;
+    const int first_bh = gi * group;
+    const int here = min(group, n_bh - first_bh);  // the last group may be smaller (and nothing follows it)
+    const int within = static_cast<int>(blockIdx.x) - gi * per_group;
+    const int rb = n_rb - 1 - within / here;
+    const int bh = first_bh + within % here;
     const int b = bh / p.H, h = bh % p.H;
     const int q0 = rb * kTileM;
     const int n = rb + 1;  // K/V tiles 0 .. rb (the last one holds the diagonal)
@@ -354,7 +363,12 @@ size_t prefill_f32_scratch_bytes(int B, int N, int H, int D) {
 }
 
 template <int kD>
-static int launch_prefill_tc_f32(const PrefillParams& p, void* scratch, void* stream) {
+static int launch_prefill_tc_f32(const PrefillParams& p_in, void* scratch, void* stream) {
+    PrefillParams p = p_in;
+    if (p.group == 0) {
+        const long long pair_bytes = 8LL * p.N * kD;  // hi and lo halves of K and V of one (sequence, head)
+        p.group = static_cast<int>(std::max<long long>(1, (32LL << 20) / pair_bytes));
+    }
     const int E = p.H * kD;
     const size_t elems = static_cast<size_t>(p.B) * p.N * E;
     const long long ctas = static_cast<long long>((p.N + tcf::kTileM - 1) / tcf::kTileM) * p.H * p.B;
