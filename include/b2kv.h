@@ -119,8 +119,8 @@ int b2kv_gather_paged(const void* pool, void* out, const int32_t* seq_lens, int 
  * with n_b = (seq_lens ? seq_lens[b] : len) + len_bias, clamped to [0, T_upper].
  * q, out are [B, H*D].  Sequences with n_b == 0 produce zeros.  The reference's limit of
  * 256 cached tokens (gpu_kv_cache.py:250-257) does not exist here: the cache is
- * processed split-K (flash decoding) and the partial results are merged by a second
- * small kernel.  T_upper is a host-side upper bound of every n_b (at most T_max); it
+ * processed split-K (flash decoding) and the partial results of a (sequence, head) are merged
+ * by the CTA that finishes its last piece.  T_upper is a host-side upper bound of every n_b (at most T_max); it
  * bounds the lengths read from the device and the size of the launch.  len_bias lets a caller attend over "length after
  * this step's append" without a separate increment of the device lengths.
  * `workspace` is scratch of at least b2kv_decode_workspace_bytes(...) bytes; it needs no

@@ -25,6 +25,7 @@ static Knob g_knobs[] = {
     {"decode_variant", 0},      // which compiled (tile, stages, warps) variant of the split kernel
     {"decode_grid_per_sm", 0},  // resident CTAs per SM to launch; 0 = occupancy
     {"decode_no_tensor_map", 0},  // 1 = row-strided caches use one bulk copy per row instead of tiled TMA loads
+    {"decode_merge_kernel", 0},  // 1 = the partials of the plain decode are merged by a second launch, not in the split kernel
     {"decode_l2_keep", 0},  // 1 = K/V bulk copies use the default L2 policy instead of evict-first
     {"prefill_force_simt", 0},  // 1 = never take the tensor-core prefill kernel
     {"prefill_variant", 0},

@@ -10,9 +10,12 @@
 // item.  Inside a CTA one producer warp streams K/V tiles from HBM into a ring of
 // shared-memory stages with bulk copies (TMA, untiled) that complete on mbarriers, and the
 // consumer warps fold each tile into an online softmax held in registers.  The producer
-// runs ahead across item boundaries, so the copy queue never drains between items.  Each
-// item leaves one partial (m, l, acc[D]) in the workspace; a small second kernel merges
-// the partials of every (sequence, head).
+// runs ahead across item boundaries, so the copy queue never drains between items.  An item
+// that is its whole (sequence, head) writes the output row itself; otherwise it leaves one partial
+// (m, l, acc[D]) in the workspace and takes a ticket for its pair, and the CTA that takes the
+// pair's last ticket merges the partials and writes the row (nobody waits for another CTA, no
+// second launch).  The forms whose merge has more to do (outputs stored into every rank's buffer,
+// unnormalised rows for the sequence split) still merge in a small second kernel.
 //
 // Arithmetic: storage type fp32 or bf16, all math in fp32; scores are kept in the log2
 // domain (q is pre-multiplied by log2(e)/sqrt(D)) so that exp is a single ex2.
@@ -22,6 +25,9 @@
 #include <math.h>
 #include <string.h>
 
+#include <atomic>
+#include <chrono>
+
 #include "b2kv_common.cuh"
 #include "tma_map.cuh"
 
@@ -30,11 +36,15 @@ namespace b2kv {
 constexpr int kFlagFirst = 1;  // first tile of an item: reset the running softmax, take q
 constexpr int kFlagLast = 2;   // last tile of an item: merge the warps and store the partial
 constexpr int kFlagDone = 4;   // no more work for this CTA
+constexpr int kFlagWhole = 8;  // the item is its whole (sequence, head): no other CTA holds a piece of it
 
 struct StageMeta {
     int slot;   // partial-result slot of the item this tile belongs to
     int ntok;   // valid rows in the tile
     int flags;
+    int pieces;          // pieces with tokens that the item's (sequence, head) was cut into, over all CTAs
+    long long pair_off;  // where the (sequence, head) starts in the token space
+    int len;             // its length
     int pad;
 };
 
@@ -72,6 +82,11 @@ struct DecodeParams {
     float q_prescale;
     GatherInfo gather;
     float* partial_out;  // non-null: the merge kernel writes (unnormalised row, max, sum) instead of the output
+    // Merge inside the split kernel (plain decode only): the CTA that finishes the last piece of a (sequence, head)
+    // merges the pair's partials and writes the output row, so that no second launch is needed.
+    void* fused_out;                 // output [B, H*D] of the storage type; null = the merge kernel writes it
+    unsigned long long* ws_tickets;  // [B*H]: (call number << 16) | pieces of the pair finished in that call
+    unsigned long long call_id;      // unique per launch, 48 bits, never 0: tickets left by other calls never count
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
@@ -97,7 +112,7 @@ struct DecodeCfg {
     static constexpr int kMergeFloats = NCW * (D + 2);
     static constexpr int kThreads = (NCW + 1) * 32;
     static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + (2 * STAGES + 2) * sizeof(uint64_t) +
-                                         STAGES * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 128;
+                                         STAGES * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 16 + 128;
     static_assert(kRowBytes % 16 == 0, "rows must be whole 16-byte chunks");
     static_assert(kChunksPerRow >= 2, "a row must span at least two lanes");
     static_assert(TILE_T % NCW == 0 && kRowsPerWarp % kRowsPerPass == 0 && kPasses % kBatch == 0, "tile split");
@@ -176,7 +191,7 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES>
 __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUtensorMap* tm_k,
                                                 const CUtensorMap* tm_v, uint8_t* stages, uint64_t* full,
-                                                uint64_t* empty, StageMeta* meta, int lane) {
+                                                uint64_t* empty, StageMeta* meta, long long* share_size, int lane) {
     const char* kbase = static_cast<const char*>(p.k);
     const char* vbase = static_cast<const char*>(p.v);
     const char* qbase = static_cast<const char*>(p.q);
@@ -187,6 +202,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
     const uint64_t l2_policy = l2_policy_evict_first();
     const Share sh = share_of(p, blockIdx.x, gridDim.x, TILE_T, lane);
+    if (lane == 0) *share_size = sh.size;  // (published to the consumers with the first stage's barrier)
     // first (sequence, head) that the share touches
     int b = p.B;
     long long tok_before = 0;  // tokens of the sequences that precede b
@@ -205,6 +221,20 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
             t_end = t_begin;
         }
         const int slot = (b * p.H + h) * p.max_seg + static_cast<int>(seg);
+        // how many CTAs hold a piece with tokens of this pair (the merge inside this kernel counts them in)
+        int pieces = 1;
+        if (p.fused_out != nullptr) {
+            const long long g_first = pair_off / sh.size, g_last = (pair_off + len_b - 1) / sh.size;
+            int cnt = 0;
+            for (long long g = g_first + lane; g <= g_last; g += 32) {
+                int t0, t1;
+                piece_of(g * sh.size, (g + 1) * sh.size, pair_off, len_b, TILE_T, t0, t1);
+                cnt += (t0 < t1) ? 1 : 0;
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+            pieces = cnt;
+        }
 
         for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
             const int ntok = min(TILE_T, t_end - t0);
@@ -218,7 +248,10 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
                 StageMeta mt;
                 mt.slot = slot;
                 mt.ntok = ntok;
-                mt.flags = (first ? kFlagFirst : 0) | (t0 + TILE_T >= t_end ? kFlagLast : 0);
+                mt.flags = (first ? kFlagFirst : 0) | (t0 + TILE_T >= t_end ? kFlagLast : 0) | (pieces == 1 ? kFlagWhole : 0);
+                mt.pieces = pieces;
+                mt.pair_off = pair_off;
+                mt.len = len_b;
                 mt.pad = 0;
                 meta[stage] = mt;
                 // a tiled load always delivers the whole box (rows past the end arrive as zeros or as
@@ -292,6 +325,9 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
             mt.slot = 0;
             mt.ntok = 0;
             mt.flags = kFlagDone;
+            mt.pieces = 0;
+            mt.pair_off = 0;
+            mt.len = 0;
             mt.pad = 0;
             meta[stage] = mt;
             mbar_arrive(&full[stage]);
@@ -312,7 +348,8 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES, int NCW>
 __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
                                                 uint64_t* empty, uint64_t* merge_bar, const StageMeta* meta,
-                                                float* merge, int warp, int lane) {
+                                                float* merge, const long long* share_size, int* verdict, int warp,
+                                                int lane) {
     constexpr int LPR = Cfg::kLanesPerRow;
     constexpr int CPL = Cfg::kChunksPerLane;
     constexpr int EPC = Cfg::kEpc;
@@ -329,6 +366,17 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
     for (int i = 0; i < NACC; ++i) {
         acc[i] = 0.f;
         qf[i] = 0.f;
+    }
+
+    // Sequences without tokens own no work item: their output rows are zeros, written here (the CTAs share them out).
+    if (p.fused_out != nullptr) {
+        T* out = static_cast<T*>(p.fused_out);
+        const int row_elems = p.H * D;
+        for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
+            if (seq_len_of(p, b) != 0) continue;
+            for (int i = warp * 32 + lane; i < row_elems; i += NCW * 32)
+                out[static_cast<size_t>(b) * row_elems + i] = Elt<T>::from_float(0.f);
+        }
     }
 
     int stage = 0;
@@ -482,6 +530,19 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                 l_all += wgt[w] * mr[w * (D + 2) + D + 1];
             }
             const int tid = warp * 32 + lane;
+            if (p.fused_out != nullptr && (mt.flags & kFlagWhole)) {
+                // the whole (sequence, head) was this one item: its row is final
+                // (divided, not multiplied by a reciprocal: bit for bit what the merge kernel gives)
+                T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(mt.slot / p.max_seg) * D;
+                for (int d = tid; d < D; d += NCW * 32) {
+                    float o = 0.f;
+#pragma unroll
+                    for (int w = 0; w < NCW; ++w) o += wgt[w] * mr[w * (D + 2) + d];
+                    orow[d] = Elt<T>::from_float(o / l_all);
+                }
+                parity ^= 1;
+                continue;
+            }
             for (int d = tid; d < D; d += NCW * 32) {
                 float o = 0.f;
 #pragma unroll
@@ -491,6 +552,65 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
             if (tid == 0) {
                 p.ws_ml[static_cast<size_t>(mt.slot) * 2] = m_all;
                 p.ws_ml[static_cast<size_t>(mt.slot) * 2 + 1] = l_all;
+            }
+            if (p.fused_out != nullptr) {
+                // One piece of several.  Publish it (fence, then the warps meet), take a ticket for the pair: the CTA
+                // that takes the pair's last ticket finds every piece in the workspace and merges them.  Nobody waits
+                // for another CTA.
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(merge_bar);
+                if (!mbar_wait(merge_bar, merge_phase)) {
+                    report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+                    return;
+                }
+                merge_phase ^= 1u;
+                const int bh = mt.slot / p.max_seg;
+                if (tid == 0) {
+                    unsigned long long* t = p.ws_tickets + bh;
+                    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(t), next;
+                    while (true) {
+                        const unsigned long long assumed = seen;
+                        next = (assumed >> 16) == p.call_id ? assumed + 1ull : ((p.call_id << 16) | 1ull);
+                        seen = atomicCAS(t, assumed, next);
+                        if (seen == assumed) break;
+                    }
+                    *verdict = (static_cast<int>(next & 0xffffull) == mt.pieces) ? 1 : 0;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(merge_bar);
+                if (!mbar_wait(merge_bar, merge_phase)) {
+                    report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+                    return;
+                }
+                merge_phase ^= 1u;
+                if (*reinterpret_cast<volatile int*>(verdict) != 0) {
+                    __threadfence();
+                    const long long size = *share_size;
+                    const long long g_first = mt.pair_off / size, g_last = (mt.pair_off + mt.len - 1) / size;
+                    const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
+                    float m_g = -INFINITY;
+                    for (long long g = g_first; g <= g_last; ++g) {
+                        int t0, t1;
+                        piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
+                        if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[(slot0 + (g - g_first)) * 2]));
+                    }
+                    T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(bh) * D;
+                    for (int d = tid; d < D; d += NCW * 32) {
+                        float l_g = 0.f, o = 0.f;
+                        for (long long g = g_first; g <= g_last; ++g) {
+                            int t0, t1;
+                            piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
+                            if (t0 < t1) {
+                                const size_t sl = slot0 + (g - g_first);
+                                const float wg = exp2f(__ldcg(&p.ws_ml[sl * 2]) - m_g);
+                                l_g += wg * __ldcg(&p.ws_ml[sl * 2 + 1]);
+                                o += wg * __ldcg(&p.ws_acc[sl * D + d]);
+                            }
+                        }
+                        orow[d] = Elt<T>::from_float(o / l_g);
+                    }
+                }
             }
             parity ^= 1;
         }
@@ -509,6 +629,8 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     uint64_t* merge_bar = empty + STAGES;  // the consumer warps meet here once per finished item
     StageMeta* meta = reinterpret_cast<StageMeta*>(empty + STAGES + 2);
     float* merge = reinterpret_cast<float*>(meta + STAGES);
+    long long* share_size = reinterpret_cast<long long*>(merge + 2 * Cfg::kMergeFloats);  // tokens per share
+    int* verdict = reinterpret_cast<int*>(share_size + 1);  // 1: this CTA took the last ticket of the pair in hand
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -521,9 +643,9 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     }
     __syncthreads();
     if (warp == NCW) {
-        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, lane);
+        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, share_size, lane);
     } else {
-        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, merge_bar, meta, merge, warp, lane);
+        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, merge_bar, meta, merge, share_size, verdict, warp, lane);
     }
 }
 
@@ -647,6 +769,15 @@ static int max_segments(int n_ctas, int H) { return (n_ctas + H - 1) / H + 2; }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Number of this launch for the tickets of the merge inside the split kernel: 48 bits, never 0, starting from a
+// value that no earlier process is likely to have left in a reused workspace.
+static unsigned long long next_call_id() {
+    static std::atomic<unsigned long long> counter{
+        (static_cast<unsigned long long>(std::chrono::steady_clock::now().time_since_epoch().count()) * 0x9E3779B97F4A7C15ull) >> 8};
+    unsigned long long id = (counter.fetch_add(1) + 1) & ((1ull << 48) - 1);
+    return id == 0 ? 1 : id;
+}
+
 template <typename T, int D, int TILE_T, int STAGES, int NCW>
 static int launch_decode(DecodeParams p, void* out, void* workspace, size_t workspace_bytes, void* stream) {
     using Cfg = DecodeCfg<T, D, TILE_T, STAGES, NCW>;
@@ -688,10 +819,17 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
 
     const size_t slots = static_cast<size_t>(p.B) * p.H * p.max_seg;
     const size_t acc_bytes = align_up(slots * D * sizeof(float), 256);
-    const size_t need = acc_bytes + slots * 2 * sizeof(float);
+    const size_t ml_bytes = align_up(slots * 2 * sizeof(float), 8);
+    const size_t need = acc_bytes + ml_bytes + static_cast<size_t>(p.B) * p.H * sizeof(unsigned long long);
     if (workspace == nullptr || workspace_bytes < need) return B2KV_ERR_WORKSPACE;
     p.ws_acc = static_cast<float*>(workspace);
     p.ws_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
+    p.ws_tickets = reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + acc_bytes + ml_bytes);
+    // The plain decode merges inside the split kernel; the forms whose merge has more to do (peer stores of the
+    // fused all-gather, unnormalised partials of the sequence split) keep the merge kernel.
+    const bool fused_merge = p.gather.peer_out == nullptr && p.partial_out == nullptr && !tune_get("decode_merge_kernel");
+    p.fused_out = fused_merge ? out : nullptr;
+    p.call_id = next_call_id();
 
     // Row-strided contiguous caches (the reference layout): one tiled TMA load per tile.  The maps
     // bound the token coordinate by T_upper, which no attended row exceeds.
@@ -711,8 +849,10 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(p, tm_k, tm_v);
     B2KV_CUDA_TRY(cudaGetLastError());
-    decode_combine_kernel<T, D><<<p.B * p.H, D < 32 ? 32 : D, 0, s>>>(p, static_cast<T*>(out), grid, TILE_T);
-    B2KV_CUDA_TRY(cudaGetLastError());
+    if (!fused_merge) {
+        decode_combine_kernel<T, D><<<p.B * p.H, D < 32 ? 32 : D, 0, s>>>(p, static_cast<T*>(out), grid, TILE_T);
+        B2KV_CUDA_TRY(cudaGetLastError());
+    }
     if (p.gather.peer_out != nullptr && p.gather.my_flags != nullptr) {
         gather_wait_kernel<<<1, 32, 0, s>>>(p.gather.my_flags, p.gather.world, p.gather.epoch, p.dev_status);
         B2KV_CUDA_TRY(cudaGetLastError());
@@ -827,7 +967,8 @@ size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype) 
     // An upper bound of what any compiled variant will ask for: the largest grid a launch uses.
     (void)T_upper;
     const size_t slots = static_cast<size_t>(B) * H * max_segments(device_sm_count() * kMaxCtasPerSm, H);
-    return align_up(slots * D * sizeof(float), 256) + slots * 2 * sizeof(float) + 256;
+    return align_up(slots * D * sizeof(float), 256) + align_up(slots * 2 * sizeof(float), 8) +
+           static_cast<size_t>(B) * H * sizeof(unsigned long long) + 256;
 }
 
 int b2kv_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens, int len,

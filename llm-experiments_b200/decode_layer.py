@@ -13,7 +13,7 @@ recompute:
     m  = gelu(h2 @ w1 + b1)                                  matmul(bias=, activation="gelu")
     y  = x2 + m @ w2 + b2                                    matmul(bias=, residual=)
 
-Seven launches per layer (the attention is two kernels), bfloat16 storage, fp32 arithmetic.  Every
+Seven launches per layer, bfloat16 storage, fp32 arithmetic.  Every
 layer owns its own ``KVCache`` object (``n_layers=1``), so that the lengths advance once per layer
 step; a ragged (per-sequence length) cache works like a shared-length one.
 """

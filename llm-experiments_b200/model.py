@@ -149,9 +149,9 @@ def decoder_state_reset(state: DecoderState) -> None:
 
 
 def launches_per_decode_step(cfg: DecoderConfig) -> int:
-    """Kernels of this library launched by one ``decode_step``: the embedding, eight per layer (the cached
-    attention is two), the final layernorm, the logits projection and the argmax."""
-    return 1 + 8 * cfg.n_layers + 3
+    """Kernels of this library launched by one ``decode_step``: the embedding, seven per layer, the final
+    layernorm, the logits projection and the argmax."""
+    return 1 + 7 * cfg.n_layers + 3
 
 
 def _head(ctx: GPUContext, state: DecoderState, rows: GPUBuffer2D, next_ids: Optional[GPUBuffer1D]) -> None:
