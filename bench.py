@@ -13,8 +13,8 @@ launched by torchrun) owns its own batch of 64 sequences and there is no collect
 step (weak scaling); time is the maximum over ranks.
 
 Rank 0 prints ONE JSON line.  ``value`` is decode tokens/s with inputs resident in HBM;
-``e2e`` is the same step through the public API with host buffers (pinned host -> device
-copies of q / new K / new V and the device -> host read of the output inside the timed
+``e2e`` is the same step through the public API with host buffers (one pinned host -> device
+copy of q, new K and new V and the device -> host read of the output inside the timed
 region); ``roofline`` is the decode kernel's algorithmic HBM bytes over its CUDA-event time
 against the measured copy bandwidth; ``cpu_baseline`` is the CPU oracle (a port of the
 reference math, all host threads) on the same 64 sequences.  Every timed loop of K steps is
@@ -363,10 +363,12 @@ def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False, assign="cont
     layer = cache.layers[0]
     for buf in (layer.k_cache.buffer, layer.v_cache.buffer):
         fill_normal(torch, buf, gen, dtype)
-    rnd = lambda: torch.randn((B, E), generator=gen, device=device, dtype=torch.float32).to(dtype)  # noqa: E731
-    q_dev, nk_dev, nv_dev = rnd(), rnd(), rnd()
+    # the step's inputs (q, new K row, new V row of every sequence) live in one buffer, so that the end-to-end
+    # step uploads them with one host -> device copy
+    qkv_dev = torch.randn((3 * B, E), generator=gen, device=device, dtype=torch.float32).to(dtype)
+    q_dev, nk_dev, nv_dev = qkv_dev[:B], qkv_dev[B:2 * B], qkv_dev[2 * B:]
     out_dev = torch.empty((B, E), device=device, dtype=dtype)
-    q_b, nk_b, nv_b, out_b = h.wrap(q_dev), h.wrap(nk_dev), h.wrap(nv_dev), h.wrap(out_dev)
+    q_b, nk_b, nv_b, out_b, qkv_b = h.wrap(q_dev), h.wrap(nk_dev), h.wrap(nv_dev), h.wrap(out_dev), h.wrap(qkv_dev)
 
     def reset_lengths():
         gpu.kv_cache_set_lengths(cache, lens0)
@@ -411,14 +413,12 @@ def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False, assign="cont
     achieved = dec_bytes / (m_dec["ms"] * 1e-3) / 1e9
 
     # ---- e2e: host buffers through the public API --------------------------------------
-    q_host, nk_host, nv_host = q_dev.cpu().pin_memory(), nk_dev.cpu().pin_memory(), nv_dev.cpu().pin_memory()
+    qkv_host = qkv_dev.cpu().pin_memory()
     out_host = torch.empty((B, E), dtype=dtype).pin_memory()
     out_host_full = torch.empty((B, H_total * D), dtype=dtype).pin_memory()
 
     def step_e2e():
-        gpu.gpu_buffer_2d_write(ctx, q_host, q_b)
-        gpu.gpu_buffer_2d_write(ctx, nk_host, nk_b)
-        gpu.gpu_buffer_2d_write(ctx, nv_host, nv_b)
+        gpu.gpu_buffer_2d_write(ctx, qkv_host, qkv_b)
         full = step_device()
         if head_split:
             out_host_full.copy_(full, non_blocking=True)
