@@ -193,7 +193,8 @@ int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* ou
  * Limits and rules:
  *   - Shapes whose partials do not fit are refused with B2KV_ERR_STATIC_LIMIT before anything is
  *     launched; use b2kv_decode with your own workspace for those.  The partials take
- *     B * H * (ceil(CTAs / H) + 2) slots of (D + 2) * 4 bytes, where CTAs is the persistent grid:
+ *     B * H * (ceil(CTAs / H) + 2) slots of (D + 2) * 4 bytes (plus 8 bytes per (sequence, head)
+ *     for the tickets), where CTAs is the persistent grid:
  *     the SM count times the resident CTAs per SM of the compiled variant (three for 256-byte
  *     rows, at most four for any row size), and never more than the tiles of work.  The
  *     benchmark shape (B=64, H=32, D=128, bf16; 444 CTAs on a 148-SM B200) needs 32768 slots
@@ -202,9 +203,11 @@ int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* ou
  *     (cudaGetSymbolAddress, with that device current).  Make that first call before starting
  *     any stream capture on that device.
  *   - All calls on one device share the one array and it keeps whatever the previous call left
- *     in it.  Nothing in it has to start at zero (each call writes every slot before reading
- *     it), but two calls that overlap on the GPU (different streams, no ordering between
- *     them) race on it: keep calls on one device in stream order.
+ *     in it.  Nothing in it has to start at zero: a call writes every partial before any CTA
+ *     reads it, and the per-(sequence, head) tickets that decide who merges carry the number of
+ *     the launch, so what an earlier call left behind never counts.  But two calls that overlap
+ *     on the GPU (different streams, no ordering between them) race on it: keep calls on one
+ *     device in stream order.
  *   - Contiguous caches only (no block table).  Results are bit-identical to b2kv_decode.
  */
 #define B2KV_STATIC_SCRATCH_BYTES (32u << 20)

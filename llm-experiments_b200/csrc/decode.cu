@@ -1094,8 +1094,8 @@ extern "C" int b2kv_decode_static(const void* q, const void* k_cache, const void
     void* scratch = nullptr;
     rc = decode_static_scratch(&scratch);
     if (rc != B2KV_OK) return rc;
-    // The partials need no clearing: every slot that the merge kernel reads is written by the
-    // split kernel of the same call first.
+    // Nothing needs clearing: every partial that a merge reads is written by the same call first, and the
+    // tickets carry the number of the launch.
     rc = decode_entry(q, k_cache, v_cache, out, seq_lens, len, len_bias, nullptr, 0, 0, 0, B, H, D, T_upper, stride_b,
                       stride_t, stride_h, dtype, scratch, static_cast<size_t>(B2KV_STATIC_SCRATCH_BYTES), dev_status,
                       stream);
