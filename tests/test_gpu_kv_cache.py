@@ -335,3 +335,23 @@ def test_decode_random_shapes_against_oracle(pkg, ctx, seed):
         if lens[b] == 0:
             assert np.all(got[b] == 0.0)
     np.testing.assert_allclose(got, want, **U.TOL[dtype])
+
+
+@pytest.mark.parametrize("B,H,T", [(1, 1, 60000), (2, 1, 40000), (1, 2, 50000), (3, 4, 9000)])
+@pytest.mark.parametrize("merge_kernel", [0, 1])
+def test_decode_one_pair_over_hundreds_of_ctas(pkg, ctx, B, H, T, merge_kernel):
+    """Few (sequence, head) pairs and long sequences: a pair is cut into hundreds of pieces (more than 255 for one
+    pair of 60000 tokens on 444 CTAs), each CTA holds one, and whoever finishes a pair's last piece merges them all.
+    With the merge inside the split kernel and with the separate merge kernel; the two agree bit for bit."""
+    D, dtype = 128, torch.bfloat16
+    lens = [T] + [T // 3] * (B - 1)
+    outs = []
+    for which in (merge_kernel, 1 - merge_kernel):
+        pkg._native.tune("decode_merge_kernel", which)
+        try:
+            got, want = _decode_case(pkg, ctx, dtype, "bhtd", 0, B=B, H=H, D=D, T_max=T, lens=lens, seed=77, poison=False)
+        finally:
+            pkg._native.tune("decode_merge_kernel", 0)
+        np.testing.assert_allclose(got, want, **U.TOL[dtype])
+        outs.append(got)
+    assert np.array_equal(outs[0], outs[1])

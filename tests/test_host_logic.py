@@ -169,3 +169,36 @@ def test_embedding_checks_like_the_reference(pkg, ctx):
         gpu.embedding(ctx, table, pos, ids, gpu.gpu_buffer_2d_create(ctx, 8, 8), 2, 4)
     with pytest.raises(RuntimeError, match="batch_begin"):
         gpu.embedding(ctx, table, pos, ids, out, 2, 4)
+
+
+def test_decoder_state_and_graphed_step_checks(pkg, ctx):
+    """model.py on CPU tensors: shapes of the state, and the checks that fire before anything is launched."""
+    import numpy as np
+
+    from llm_experiments_b200 import model
+
+    cfg = model.DecoderConfig(vocab_size=64, context_size=32, embedding_dim=128, n_heads=1, n_layers=2)
+    pe = model.positional_encoding(cfg.context_size, cfg.embedding_dim)
+    assert pe.shape == (32, 128) and pe[0, 0] == 0.0 and pe[0, 1] == 1.0  # sin(0), cos(0) interleaved
+    E, V = cfg.embedding_dim, cfg.vocab_size
+    z = lambda *shape: np.zeros(shape, dtype=np.float32)  # noqa: E731
+    layer = dict(ln1_gamma=z(E), ln1_beta=z(E), wq=z(E, E), wk=z(E, E), wv=z(E, E), wo=z(E, E), ln2_gamma=z(E),
+                 ln2_beta=z(E), w1=z(E, 4 * E), b1=z(4 * E), w2=z(4 * E, E), b2=z(E))
+    params = dict(embedding=z(V, E), pos_encoding=pe, layers=[layer, layer], lnf_gamma=z(E), lnf_beta=z(E),
+                  out_proj=z(E, V))
+    weights = model.weights_from_numpy(ctx, cfg, params)
+    assert weights.out_proj.shape == (E, V) and weights.layers[1].w1.buffer.dtype == torch.bfloat16
+    state = model.decoder_state_create(ctx, cfg, weights, batch_size=3)
+    assert len(state.caches) == 2 and state.logits.shape == (3, V) and state.caches[0].layout == "bhtd"
+    assert model.launches_per_decode_step(cfg) == 1 + 7 * 2 + 3
+    with pytest.raises(ValueError, match="exceeds context size"):
+        model.decoder_state_create(ctx, cfg, weights, batch_size=3, max_seq_len=33)
+    with pytest.raises(ValueError, match="ragged=True"):
+        model.GraphedDecodeStep(ctx, state)  # lengths must live on the device
+    tok = pkg.gpu.gpu_buffer_1d_create(ctx, 3, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="batch_begin"):
+        model.decode_step(ctx, state, tok)
+    for cache in state.caches:
+        cache.current_len = 32
+    with pytest.raises(ValueError, match="Cache is full"):
+        model.decode_step(ctx, state, tok)
