@@ -86,7 +86,8 @@ struct DecodeParams {
     // merges the pair's partials and writes the output row, so that no second launch is needed.
     void* fused_out;                 // output [B, H*D] of the storage type; null = the merge kernel writes it
     unsigned long long* ws_tickets;  // [B*H]: (call number << 16) | pieces of the pair finished in that call
-    unsigned long long call_id;      // unique per launch, 48 bits, never 0: tickets left by other calls never count
+    unsigned long long call_id;      // unique per launch call, 48 bits, never 0: tickets left by other calls never count
+                                     // (a finished pair's ticket goes back to 0, for launches replayed from a graph)
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
@@ -610,6 +611,10 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                         }
                         orow[d] = Elt<T>::from_float(o / l_g);
                     }
+                    // Every piece of the pair has come in, so nobody touches its ticket again in this launch: leave
+                    // it at zero.  A launch replayed from a CUDA graph carries the number it was captured with, and
+                    // must not count on top of its own earlier run.
+                    if (tid == 0) p.ws_tickets[bh] = 0ull;
                 }
             }
             parity ^= 1;

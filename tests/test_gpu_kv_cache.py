@@ -355,3 +355,48 @@ def test_decode_one_pair_over_hundreds_of_ctas(pkg, ctx, B, H, T, merge_kernel):
         np.testing.assert_allclose(got, want, **U.TOL[dtype])
         outs.append(got)
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_decode_replayed_from_a_cuda_graph(pkg, ctx):
+    """A decode launch captured into a CUDA graph and replayed with new queries and new lengths (both on the device):
+    every replay equals the eager call on the same inputs, bit for bit, although the replays carry the launch number
+    they were captured with.  Few pairs and long sequences, so every pair is cut over many CTAs and merged through
+    the tickets in the workspace."""
+    gpu = pkg.gpu
+    B, H, D, T, dtype = 2, 2, 128, 20000, torch.bfloat16
+    E = H * D
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=dtype, layout="bhtd", ragged=True))
+    cache.layers[0].k_cache.buffer.copy_(U.randn((B * H * T, D), dtype, ctx.device, 1))
+    cache.layers[0].v_cache.buffer.copy_(U.randn((B * H * T, D), dtype, ctx.device, 2))
+    gpu.kv_cache_set_lengths(cache, [T, T // 2])
+    cache.current_len = T  # the upper bound that sizes the launch stays fixed
+    q, out = U.randn((B, E), dtype, ctx.device, 3), torch.empty((B, E), dtype=dtype, device=ctx.device)
+    qb, ob = U.buf2d(pkg, ctx, q), U.buf2d(pkg, ctx, out)
+
+    def launch():
+        gpu.batch_begin(ctx)
+        gpu.attention_with_kv_cache(ctx, cache, 0, qb, ob)
+        gpu.batch_commit(ctx)
+
+    side = torch.cuda.Stream(device=ctx.device)
+    side.wait_stream(torch.cuda.current_stream(ctx.device))
+    with torch.cuda.stream(side):
+        launch()  # first-use set-up outside the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            launch()
+    torch.cuda.current_stream(ctx.device).wait_stream(side)
+    for i, lens in enumerate([[T, T // 2], [777, T], [T - 1, 1], [12345, 6789]]):
+        q.copy_(U.randn((B, E), dtype, ctx.device, 10 + i))
+        cache.seq_lens.copy_(torch.tensor(lens, dtype=torch.int32))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = out.clone()
+        launch()
+        torch.cuda.synchronize()
+        assert torch.equal(replayed.view(torch.int16), out.view(torch.int16)), f"replay {i}"
+        k4 = cache.layers[0].k_cache.buffer.view(B, H, T, D).permute(0, 2, 1, 3)
+        v4 = cache.layers[0].v_cache.buffer.view(B, H, T, D).permute(0, 2, 1, 3)
+        want = U.oracle_decode(q, k4.contiguous(), v4.contiguous(), lens)
+        np.testing.assert_allclose(U.to_f32(replayed), want, **U.TOL[dtype])
