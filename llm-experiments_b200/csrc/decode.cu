@@ -239,6 +239,13 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
         for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
             const int ntok = min(TILE_T, t_end - t0);
+            // paged: this lane's block of the tile is looked up before the wait for a free stage, so that the table's
+            // latency falls into that wait and not between a stage coming free and its copies going out
+            int blk_ahead = -1;
+            if (p.block_table != nullptr && !p.use_tensor_map) {
+                const int tok = t0 + lane * p.run_len;
+                if (tok < t0 + ntok) blk_ahead = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+            }
             if (!mbar_wait(&empty[stage], phase ^ 1u)) {
                 ok = false;
                 break;
@@ -284,7 +291,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
                 if (p.block_table == nullptr) {
                     off = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(tok) * p.stride_t;
                 } else {
-                    int blk = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+                    int blk = r == lane ? blk_ahead : p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
                     if (blk < 0 || blk >= p.n_blocks) {
                         report_status(p.dev_status, B2KV_DEV_BAD_BLOCK);
                         blk = 0;  // stay inside the pool; the status word tells the caller
