@@ -356,7 +356,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES, int NCW>
 __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
                                                 uint64_t* empty, uint64_t* merge_bar, const StageMeta* meta,
-                                                float* merge, const long long* share_size, int* verdict, int warp,
+                                                float* merge, const long long* share_size, int* merge_here, int warp,
                                                 int lane) {
     constexpr int LPR = Cfg::kLanesPerRow;
     constexpr int CPL = Cfg::kChunksPerLane;
@@ -583,7 +583,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                         seen = atomicCAS(t, assumed, next);
                         if (seen == assumed) break;
                     }
-                    *verdict = (static_cast<int>(next & 0xffffull) == mt.pieces) ? 1 : 0;
+                    *merge_here = (static_cast<int>(next & 0xffffull) == mt.pieces) ? 1 : 0;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(merge_bar);
@@ -592,7 +592,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                     return;
                 }
                 merge_phase ^= 1u;
-                if (*reinterpret_cast<volatile int*>(verdict) != 0) {
+                if (*reinterpret_cast<volatile int*>(merge_here) != 0) {
                     __threadfence();
                     const long long size = *share_size;
                     const long long g_first = mt.pair_off / size, g_last = (mt.pair_off + mt.len - 1) / size;
@@ -642,7 +642,7 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     StageMeta* meta = reinterpret_cast<StageMeta*>(empty + STAGES + 2);
     float* merge = reinterpret_cast<float*>(meta + STAGES);
     long long* share_size = reinterpret_cast<long long*>(merge + 2 * Cfg::kMergeFloats);  // tokens per share
-    int* verdict = reinterpret_cast<int*>(share_size + 1);  // 1: this CTA took the last ticket of the pair in hand
+    int* merge_here = reinterpret_cast<int*>(share_size + 1);  // 1: this CTA took the last ticket of the pair in hand
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -657,7 +657,7 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     if (warp == NCW) {
         decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, share_size, lane);
     } else {
-        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, merge_bar, meta, merge, share_size, verdict, warp, lane);
+        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, merge_bar, meta, merge, share_size, merge_here, warp, lane);
     }
 }
 
