@@ -26,6 +26,13 @@
  *   alignment    every pointer 16-byte aligned, D*sizeof(element) a multiple of 16,
  *                every stride*sizeof(element) a multiple of 16.
  *   stream       a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   overlap      the kernels of a decode step (append, Q/K/V projection, decode, row products,
+ *                layernorm, length advance) are launched with programmatic stream
+ *                serialisation: each may be scheduled while the kernel before it in the
+ *                stream is still running, sets itself up (and streams the first weight
+ *                tiles, which no kernel writes), and waits for that kernel to complete
+ *                before it reads anything else or writes at all.  Results are those of
+ *                plain stream order; b2kv_tune("serial_launches", 1) switches it off.
  *   return       0 on success, a negative B2KV_ERR_* code otherwise; nothing is
  *                launched when an argument check fails.
  *   dev_status   optional int32 device word (NULL to skip).  A kernel that detects a
@@ -86,6 +93,14 @@ int b2kv_append_paged(const void* new_k, const void* new_v, void* k_pool, void* 
                       int advance, const int32_t* block_table, int max_blocks, int block_size, int n_blocks, int B,
                       int H, int D, int64_t stride_blk, int64_t stride_t, int64_t stride_h, int dtype,
                       int32_t* dev_status, void* stream);
+
+/*
+ * seq_lens[b] += delta for b < B, in stream order: the length bookkeeping of a ragged cache after an append that did
+ * not advance it (b2kv_qkv_append; b2kv_append with advance = 0).  The reference keeps one host-side current_len
+ * and adds one in kv_cache_update (simple-llm/src/gpu/gpu_kv_cache.py:186); per-sequence device lengths have no
+ * counterpart there.
+ */
+int b2kv_advance_lengths(int32_t* seq_lens, int B, int delta, void* stream);
 
 /*
  * A whole prompt into a paged cache: rows [b * n_rows + i] of k_rows / v_rows ([B * n_rows, H * D], the layout
@@ -355,6 +370,7 @@ int b2kv_matmul(const void* a, const void* w, const void* bias, const void* resi
  * fills the pool with the copy kernel, "prefill_test_expire": 1 = test hook, the softmax warps of the one-CTA tensor-core prefill
  * behave as if their first bounded wait had run out (the launch then ends after about two seconds with
  * B2KV_DEV_WAIT_TIMEOUT in dev_status), "matmul_splits": ranges of input features per tile in b2kv_matmul_rows,
+ * "serial_launches": 1 = plain stream order for every launch (see "overlap" at the top),
  * "gemm_variant": 1 = one CTA per output tile, 2 / 3 = CTA pairs with 64 / 128 input features per
  * ring stage in b2kv_matmul);
  * returns B2KV_ERR_BAD_ARG

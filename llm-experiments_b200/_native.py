@@ -43,6 +43,7 @@ SIGNATURES = {
     "b2kv_append_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i,
                                _vp, _vp]),
     "b2kv_append_rows_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
+    "b2kv_advance_lengths": (_i, [_vp, _i, _i, _vp]),
     "b2kv_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp]),
     "b2kv_gather_paged": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "b2kv_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

@@ -4,6 +4,8 @@
 // (simple-llm/src/gpu/gpu_kernels.py:2725-2798): one thread there copies one float of K
 // and one of V; here one thread copies one 16-byte chunk of each, for any storage type,
 // any cache layout given by strides, and optionally through a block table.
+#include <algorithm>
+
 #include "b2kv_common.cuh"
 
 namespace b2kv {
@@ -47,6 +49,9 @@ __global__ void __launch_bounds__(1024) append_kernel(const uint4* __restrict__ 
                                                       uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
                                                       RowMap m, int32_t* seq_rw, int advance, int H, int D,
                                                       int chunks_per_row, int shift) {
+    grid_launch_dependents();
+    if (threadIdx.x == 0) grid_dependency_wait();  // the new rows and the positions may come from the kernel before this one
+    __syncthreads();
     const int b = blockIdx.x;
     const int t = seq_rw ? seq_rw[b] : m.scalar;
     const int64_t base = row_offset(m, b, t);
@@ -66,6 +71,15 @@ __global__ void __launch_bounds__(1024) append_kernel(const uint4* __restrict__ 
         __syncthreads();
         if (threadIdx.x == 0 && base >= 0) seq_rw[b] = t + 1;
     }
+}
+
+// seq[b] += delta for b < B: the lengths of a ragged cache after a kernel that appended without advancing them.
+__global__ void __launch_bounds__(1024) advance_kernel(int32_t* seq, int B, int delta) {
+    grid_launch_dependents();
+    if (threadIdx.x == 0) grid_dependency_wait();  // the kernel before this one still reads the old lengths
+    __syncthreads();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) seq[b] += delta;
 }
 
 // Many rows per sequence (a prompt): grid (n_rows, B); rows[b * src_rows_per_seq + src_first + i] goes to position
@@ -126,10 +140,10 @@ static int launch_append(const void* new_k, const void* new_v, void* k_cache, vo
     const int shift = es == 4 ? 2 : 3;
     int threads = (chunks + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
-    append_kernel<<<B, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(new_k), static_cast<const uint4*>(new_v), static_cast<uint4*>(k_cache),
-        static_cast<uint4*>(v_cache), m, seq_rw, advance, H, D, chunks, shift);
-    B2KV_CUDA_TRY(cudaGetLastError());
+    OverlapLaunch launch(B, threads, 0, stream);
+    B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, append_kernel, static_cast<const uint4*>(new_k),
+                                     static_cast<const uint4*>(new_v), static_cast<uint4*>(k_cache),
+                                     static_cast<uint4*>(v_cache), m, seq_rw, advance, H, D, chunks, shift));
     return B2KV_OK;
 }
 
@@ -223,6 +237,14 @@ int b2kv_append_paged(const void* new_k, const void* new_v, void* k_pool, void* 
     if (seq_pos == nullptr && (pos < 0 || pos >= max_blocks * block_size)) return B2KV_ERR_BAD_ARG;
     RowMap m{seq_pos, pos, block_table, max_blocks, block_size, n_blocks, stride_blk, stride_t, stride_h, 0, dev_status};
     return launch_append(new_k, new_v, k_pool, v_pool, m, seq_pos, advance, B, H, D, dtype, stream);
+}
+
+int b2kv_advance_lengths(int32_t* seq_lens, int B, int delta, void* stream) {
+    if (seq_lens == nullptr || B <= 0) return B2KV_ERR_BAD_ARG;
+    const int threads = std::min(1024, (B + 31) / 32 * 32);
+    OverlapLaunch launch((B + threads - 1) / threads, threads, 0, stream);
+    B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, advance_kernel, seq_lens, B, delta));
+    return B2KV_OK;
 }
 
 int b2kv_append_rows_paged(const void* k_rows, const void* v_rows, void* k_pool, void* v_pool, const int32_t* block_table,

@@ -30,6 +30,36 @@ inline bool stride_ok(int64_t s, int es) { return s >= 0 && ((s * es) & 15) == 0
 int tune_get(const char* name);
 int device_sm_count();
 
+// Launch configuration of a kernel that takes part in programmatic dependent launch: the grid may be
+// scheduled while the kernel before it in the stream is still running, as soon as every CTA of that
+// kernel has executed grid_launch_dependents() (or has exited); nothing of what the earlier kernels wrote
+// may be read, and nothing written, before grid_dependency_wait() returns.  A kernel launched this way
+// must execute grid_dependency_wait() on every path, or kernels after it could overtake kernels before it.
+// The knob "serial_launches" != 0 leaves the attribute out (plain stream order).
+struct OverlapLaunch {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    OverlapLaunch(dim3 grid, dim3 block, size_t smem, void* stream, unsigned cluster_x = 1) : cfg{}, attr{} {
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cfg.attrs = attr;
+        if (cluster_x > 1) {
+            attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+            attr[cfg.numAttrs].val.clusterDim.x = cluster_x;
+            attr[cfg.numAttrs].val.clusterDim.y = 1;
+            attr[cfg.numAttrs].val.clusterDim.z = 1;
+            ++cfg.numAttrs;
+        }
+        if (tune_get("serial_launches") == 0) {
+            attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+            ++cfg.numAttrs;
+        }
+    }
+};
+
 // ---------------------------------------------------------------------------------------
 // storage types: 16-byte chunks widened to float
 // ---------------------------------------------------------------------------------------
@@ -167,6 +197,12 @@ template <int kThreads>
 __device__ __forceinline__ void named_barrier_sync(int id) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kThreads) : "memory");
 }
+
+// Programmatic dependent launch, device side (no-ops in a kernel launched in plain stream order).
+// wait: returns when every kernel before this one in the stream has completed and its writes are visible.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// launch_dependents: this CTA no longer holds back the start of the next kernel in the stream.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void report_status(int32_t* dev_status, int code) {
     if (dev_status != nullptr) atomicCAS(dev_status, 0, code);

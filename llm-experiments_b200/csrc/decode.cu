@@ -200,6 +200,8 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
     uint32_t phase = 0;
     long long fills = 0;  // stages filled so far (for the drain after a failed wait)
     bool ok = true;
+    bool let_go = false;  // grid_launch_dependents() has been executed
+    constexpr int kLetGoTiles = 8;
 
     const uint64_t l2_policy = l2_policy_evict_first();
     const Share sh = share_of(p, blockIdx.x, gridDim.x, TILE_T, lane);
@@ -239,6 +241,14 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
         for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
             const int ntok = min(TILE_T, t_end - t0);
+            // A few tiles before the end of the share the next kernel in the stream may be scheduled (it waits
+            // for the end of this grid before it reads or writes anything): its launch then costs no time between
+            // the two.  Not earlier: CTAs that wait next to streaming ones for the whole launch were measured to
+            // slow those down (the step went from 0.67 to 0.82 ms).
+            if (!let_go && sh.end - (pair_off + t0) <= kLetGoTiles * TILE_T) {
+                grid_launch_dependents();
+                let_go = true;
+            }
             // paged: this lane's block of the tile is looked up before the wait for a free stage, so that the table's
             // latency falls into that wait and not between a stage coming free and its copies going out
             int blk_ahead = -1;
@@ -327,6 +337,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
         }
     }
 
+    if (!let_go) grid_launch_dependents();
     if (ok && mbar_wait(&empty[stage], phase ^ 1u)) {
         if (lane == 0) {
             StageMeta mt;
@@ -652,6 +663,10 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
         }
         mbar_init(merge_bar, NCW);
         fence_mbar_init();
+        // The lengths, the queries and the newest cache rows may come from the kernel before this one.  One thread
+        // waits for it and the others sleep at the barrier: a CTA that is launched ahead of time shares its SM
+        // with CTAs of that kernel and must not take issue slots from them.
+        grid_dependency_wait();
     }
     __syncthreads();
     if (warp == NCW) {
@@ -859,7 +874,8 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     }
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(p, tm_k, tm_v);
+    OverlapLaunch launch(grid, Cfg::kThreads, Cfg::kSmemBytes, s);
+    B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, kernel, p, tm_k, tm_v));
     B2KV_CUDA_TRY(cudaGetLastError());
     if (!fused_merge) {
         decode_combine_kernel<T, D><<<p.B * p.H, D < 32 ? 32 : D, 0, s>>>(p, static_cast<T*>(out), grid, TILE_T);

@@ -132,6 +132,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     const int n_st = p.stages;
     const uint32_t stage_bytes = kWBytes + 2 * x_span;
 
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStagesP; ++s) {
             mbar_init(&sm.full[s], 1);
@@ -147,7 +148,13 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
         tmem_relinquish();
         tc_fence_before();
     }
+    // Launched ahead of the end of the kernel before it: only the weights, which no kernel writes, are
+    // touched before that kernel is complete.  The copy warp waits after it has asked for the ring's
+    // first weight tiles; one thread waits for the epilogue warps (positions, residual, outputs); the
+    // issuing warp touches shared and tensor memory only.
     if (threadIdx.x < kMaxBatch) {
+        if (threadIdx.x == 0) grid_dependency_wait();
+        named_barrier_sync<kMaxBatch>(2);
         // where sequence b's values go: its row of q_out, or its new row of the cache
         const int b = threadIdx.x;
         long long row = -1;
@@ -168,17 +175,31 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     if (warp == 4) {
         if (lane == 0) {
             const CUtensorMap* tw = which == 0 ? &tm_wq : (which == 1 ? &tm_wk : &tm_wv);
-            for (int i = 0; i < n_k; ++i) {
+            // W tile: input features k0 .. +127 (rows), output features c0 .. c0+127 as two 64-wide boxes
+            auto load_w = [&](int st, int k0) {
+                tma_load_2d(w_ring + st * kWBytes, tw, &sm.full[st], c0, k0);
+                tma_load_2d(w_ring + st * kWBytes + kWHalf, tw, &sm.full[st], c0 + 64, k0);
+            };
+            // x tile: every sequence (rows past B read as zero), two 64-feature spans
+            auto load_x = [&](int st, int k0) {
+                tma_load_2d(x_ring + st * 2 * x_span, &tm_x, &sm.full[st], k0, 0);
+                tma_load_2d(x_ring + st * 2 * x_span + x_span, &tm_x, &sm.full[st], k0 + 64, 0);
+            };
+            // the ring starts empty: its first round of weight tiles is on its way before x may be read
+            const int ahead = n_k < n_st ? n_k : n_st;
+            for (int i = 0; i < ahead; ++i) {
+                mbar_arrive_expect_tx(&sm.full[i], stage_bytes);
+                load_w(i, (k_first + i) * kKTile);
+            }
+            grid_dependency_wait();
+            for (int i = 0; i < ahead; ++i) load_x(i, (k_first + i) * kKTile);
+            for (int i = ahead; i < n_k; ++i) {
                 const int st = i % n_st;
                 if (!mbar_wait(&sm.empty[st], ((i / n_st) & 1) ^ 1)) break;
                 mbar_arrive_expect_tx(&sm.full[st], stage_bytes);
                 const int k0 = (k_first + i) * kKTile;
-                // W tile: input features k0 .. +127 (rows), output features c0 .. c0+127 as two 64-wide boxes
-                tma_load_2d(w_ring + st * kWBytes, tw, &sm.full[st], c0, k0);
-                tma_load_2d(w_ring + st * kWBytes + kWHalf, tw, &sm.full[st], c0 + 64, k0);
-                // x tile: every sequence (rows past B read as zero), two 64-feature spans
-                tma_load_2d(x_ring + st * 2 * x_span, &tm_x, &sm.full[st], k0, 0);
-                tma_load_2d(x_ring + st * 2 * x_span + x_span, &tm_x, &sm.full[st], k0 + 64, 0);
+                load_w(st, k0);
+                load_x(st, k0);
             }
         }
         __syncwarp();
@@ -355,9 +376,8 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
     B2KV_CUDA_TRY(proj::configure_smem(dev, smem));
-    proj::qkv_append_kernel<<<3 * E / proj::kFeat, proj::kProjThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv,
-                                                                                                                   tx, p);
-    B2KV_CUDA_TRY(cudaGetLastError());
+    OverlapLaunch launch(3 * E / proj::kFeat, proj::kProjThreads, smem, stream);
+    B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, proj::qkv_append_kernel, tq, tk, tv, tx, p));
     return B2KV_OK;
 }
 
@@ -389,19 +409,7 @@ extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* bias, 
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
     B2KV_CUDA_TRY(proj::configure_smem(dev, smem));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles * splits);
-    cfg.blockDim = dim3(proj::kProjThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;  // the CTAs of one tile
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    B2KV_CUDA_TRY(cudaLaunchKernelEx(&cfg, proj::qkv_append_kernel, tw, tw, tw, tx, p));
-    B2KV_CUDA_TRY(cudaGetLastError());
+    OverlapLaunch launch(tiles * splits, proj::kProjThreads, smem, stream, splits);  // cluster = the CTAs of one tile
+    B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, proj::qkv_append_kernel, tw, tw, tw, tx, p));
     return B2KV_OK;
 }

@@ -78,6 +78,9 @@ __global__ void __launch_bounds__(kCtaThreads) row_kernel(const T* __restrict__ 
                                                          const T* __restrict__ be, T* __restrict__ y,
                                                          int64_t rows, int size, float eps) {
     __shared__ float scratch[kCtaThreads / 32];
+    grid_launch_dependents();
+    if (threadIdx.x == 0) grid_dependency_wait();  // the rows come from the kernel before this one
+    __syncthreads();
     constexpr int kRowsPerCta = kCtaThreads / kTpr;
     const int t = threadIdx.x % kTpr;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + threadIdx.x / kTpr;
@@ -164,13 +167,13 @@ int launch_rows(const T* x, const T* ga, const T* be, T* y, int64_t rows, int si
     const int64_t ctas = (rows + kCtaThreads / tpr - 1) / (kCtaThreads / tpr);
     if (ctas > 0x7fffffffLL) return B2KV_ERR_UNSUPPORTED;
     const unsigned grid = static_cast<unsigned>(ctas);
+    OverlapLaunch launch(grid, kCtaThreads, 0, stream);
     switch (tpr) {
-        case 32: row_kernel<kMode, 32, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
-        case 64: row_kernel<kMode, 64, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
-        case 128: row_kernel<kMode, 128, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
-        default: row_kernel<kMode, 256, T><<<grid, kCtaThreads, 0, stream>>>(x, ga, be, y, rows, size, eps); break;
+        case 32: B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, row_kernel<kMode, 32, T>, x, ga, be, y, rows, size, eps)); break;
+        case 64: B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, row_kernel<kMode, 64, T>, x, ga, be, y, rows, size, eps)); break;
+        case 128: B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, row_kernel<kMode, 128, T>, x, ga, be, y, rows, size, eps)); break;
+        default: B2KV_CUDA_TRY(cudaLaunchKernelEx(&launch.cfg, row_kernel<kMode, 256, T>, x, ga, be, y, rows, size, eps)); break;
     }
-    B2KV_CUDA_TRY(cudaGetLastError());
     return B2KV_OK;
 }
 

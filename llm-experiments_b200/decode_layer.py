@@ -13,7 +13,10 @@ recompute:
     m  = gelu(h2 @ w1 + b1)                                  matmul(bias=, activation="gelu")
     y  = x2 + m @ w2 + b2                                    matmul(bias=, residual=)
 
-Seven launches per layer, bfloat16 storage, fp32 arithmetic.  Every
+Seven launches per layer (eight with a ragged cache, whose device-side lengths a small kernel advances after the
+projection), bfloat16 storage, fp32 arithmetic.  Each launch is scheduled ahead of the end of the one before it
+and waits inside the kernel for that one to complete; the weight-streaming kernels ask for their first weight
+tiles before that wait.  Every
 layer owns its own ``KVCache`` object (``n_layers=1``), so that the lengths advance once per layer
 step; a ragged (per-sequence length) cache works like a shared-length one.
 """

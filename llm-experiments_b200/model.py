@@ -149,9 +149,10 @@ def decoder_state_reset(state: DecoderState) -> None:
 
 
 def launches_per_decode_step(cfg: DecoderConfig) -> int:
-    """Kernels of this library launched by one ``decode_step``: the embedding, seven per layer, the final
-    layernorm, the logits projection and the argmax."""
-    return 1 + 7 * cfg.n_layers + 3
+    """Kernels of this library launched by one ``decode_step``: the embedding, eight per layer (seven operations
+    and the advance of the layer cache's device-side lengths), the final layernorm, the logits projection and the
+    argmax."""
+    return 1 + 8 * cfg.n_layers + 3
 
 
 def _head(ctx: GPUContext, state: DecoderState, rows: GPUBuffer2D, next_ids: Optional[GPUBuffer1D]) -> None:

@@ -94,5 +94,6 @@ def qkv_project_append(ctx: GPUContext, cache: KVCache, layer_idx: int, x: GPUBu
     _native.check(rc)
     if advance:
         if cache.seq_lens is not None:
-            cache.seq_lens.add_(1)  # stream-ordered after the kernel, which read the old positions
+            # stream-ordered after the kernel, which read the old positions
+            _native.check(_native.lib.b2kv_advance_lengths(cache.seq_lens.data_ptr(), cache.batch_size, 1, stream))
         cache.current_len += 1

@@ -157,3 +157,64 @@ def test_prompt_layer_step_vs_oracle_then_decode_continues(pkg, B, N, H, D):
                                                            np.full(B, N, dtype=np.int32), H)
     np.testing.assert_allclose(U.to_f32(y1), want_y1, rtol=2.0 ** -6, atol=3e-2)
     assert cache.current_len == N + 1
+
+
+def test_overlapped_launches_give_the_results_of_plain_stream_order(pkg):
+    """The kernels of a decode step are launched ahead of the end of the kernel before them and wait inside for
+    it.  Three layers over eight steps, queued without a host synchronisation, must leave bit for bit the rows
+    and caches that the same chain leaves when every launch is in plain stream order (knob ``serial_launches``)."""
+    from llm_experiments_b200 import _native, decode_layer
+
+    gpu = pkg.gpu
+    B, H, D, T_max, n_layers, n_steps = 24, 8, 128, 2048, 3, 8
+    E = H * D
+
+    def run(serial):
+        _native.tune("serial_launches", 1 if serial else 0)
+        try:
+            ctx = U.make_ctx(pkg)
+            g = torch.Generator().manual_seed(11)
+            rnd = lambda shape, scale=1.0: (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(ctx.device)  # noqa: E731
+            b2 = lambda t: gpu.GPUBuffer2D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+            b1 = lambda t: gpu.GPUBuffer1D(buffer=t, shape=tuple(t.shape), size=t.numel())  # noqa: E731
+            weights, caches = [], []
+            lens = np.random.default_rng(5).integers(100, T_max - n_steps - 1, size=B).astype(np.int32)
+            for _ in range(n_layers):
+                raw = dict(ln1_gamma=rnd((E,), 0.2) + 1, ln1_beta=rnd((E,), 0.1), wq=rnd((E, E), E ** -0.5),
+                           wk=rnd((E, E), E ** -0.5), wv=rnd((E, E), E ** -0.5), wo=rnd((E, E), E ** -0.5),
+                           ln2_gamma=rnd((E,), 0.2) + 1, ln2_beta=rnd((E,), 0.1), w1=rnd((E, 4 * E), E ** -0.5),
+                           b1=rnd((4 * E,), 0.1), w2=rnd((4 * E, E), (4 * E) ** -0.5), b2=rnd((E,), 0.1))
+                weights.append(decode_layer.DecoderLayerWeights(**{k: (b1(v) if v.dim() == 1 else b2(v)) for k, v in raw.items()}))
+                cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T_max, n_layers=1, n_heads=H,
+                                                                   head_dim=D, dtype=torch.bfloat16, layout="bhtd",
+                                                                   ragged=True))
+                cache.layers[0].k_cache.buffer.copy_(rnd(tuple(cache.layers[0].k_cache.buffer.shape)))
+                cache.layers[0].v_cache.buffer.copy_(rnd(tuple(cache.layers[0].v_cache.buffer.shape)))
+                gpu.kv_cache_set_lengths(cache, lens)
+                caches.append(cache)
+            scratch = decode_layer.decoder_layer_scratch(ctx, B, E)
+            bufs = [rnd((B, E))] + [torch.empty((B, E), dtype=torch.bfloat16, device=ctx.device) for _ in range(n_layers)]
+            outs = []
+            for _ in range(n_steps):
+                gpu.batch_begin(ctx)
+                for li in range(n_layers):
+                    decode_layer.decoder_layer_step(ctx, caches[li], b2(bufs[li]), weights[li], scratch, b2(bufs[li + 1]))
+                gpu.batch_commit(ctx)
+                outs.append(bufs[n_layers].clone())
+                bufs[0].copy_(bufs[n_layers])  # the next step's rows are this step's output
+            torch.cuda.synchronize()
+            assert int(ctx.dev_status.item()) == 0
+            state = [t.view(torch.int16).cpu() for t in outs]
+            for c in caches:
+                state.append(c.layers[0].k_cache.buffer.view(torch.int16).cpu())
+                state.append(c.layers[0].v_cache.buffer.view(torch.int16).cpu())
+                state.append(c.seq_lens.cpu())
+            return state
+        finally:
+            _native.tune("serial_launches", 0)
+
+    overlapped, serial = run(False), run(True)
+    assert len(overlapped) == len(serial)
+    for a, b in zip(overlapped, serial):
+        assert torch.equal(a, b)
+    assert not torch.equal(overlapped[0], overlapped[n_steps - 1])  # the steps did something

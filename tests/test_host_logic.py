@@ -190,7 +190,7 @@ def test_decoder_state_and_graphed_step_checks(pkg, ctx):
     assert weights.out_proj.shape == (E, V) and weights.layers[1].w1.buffer.dtype == torch.bfloat16
     state = model.decoder_state_create(ctx, cfg, weights, batch_size=3)
     assert len(state.caches) == 2 and state.logits.shape == (3, V) and state.caches[0].layout == "bhtd"
-    assert model.launches_per_decode_step(cfg) == 1 + 7 * 2 + 3
+    assert model.launches_per_decode_step(cfg) == 1 + 8 * 2 + 3
     with pytest.raises(ValueError, match="exceeds context size"):
         model.decoder_state_create(ctx, cfg, weights, batch_size=3, max_seq_len=33)
     with pytest.raises(ValueError, match="ragged=True"):
