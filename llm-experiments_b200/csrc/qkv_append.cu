@@ -26,12 +26,14 @@
 // bias, the reference's GELU and a residual applied before rounding.
 //
 // A matrix with few output features (N = E: 32 tiles at E = 4096) would keep only a few SMs streaming.
-// Its input features are then cut into `splits` ranges; the CTAs of a tile form a thread-block cluster,
-// each leaves its fp32 partial tile in its own shared memory (the ring is idle by then), and after a
-// cluster barrier every CTA adds up, in range order, a share of the sequences straight from its peers'
-// shared memory (distributed shared memory) and writes those outputs.  No partial goes to global
-// memory and the sum does not depend on timing.  (With enough tiles to fill the machine - the fused
-// Q/K/V form - splitting was measured slower and is not used.)
+// Its input features are then cut into `splits` ranges; the CTAs of a tile form a thread-block cluster.
+// Every CTA owns a share of the sequences (b mod splits); when its products are done a CTA stores each
+// sequence's fp32 partial values into the owner's shared memory (distributed shared memory: stores are
+// not waited for, unlike loads from a peer, which cost about 0.7 us each here), and after one cluster
+// barrier every CTA adds up its own sequences' partials, in range order, from its own shared memory and
+// writes those outputs.  No partial goes to global memory and the sum does not depend on timing.  (With
+// enough tiles to fill the machine - the fused Q/K/V form - splitting was measured slower and is not
+// used.)
 #include <algorithm>
 
 #include "b2kv_common.cuh"
@@ -51,6 +53,7 @@ constexpr int kFeat = 128;      // output features per CTA (MMA M)
 constexpr int kKTile = 128;
 constexpr int kMaxStagesP = 6;
 constexpr int kRingBytes = 200 * 1024;  // shared memory given to the ring; as many stages as fit
+constexpr int kSmemBytes = 224 * 1024;  // ring and partials of a split tile together (227 KB less alignment and statics)
 constexpr int kWBytes = kKTile * kFeat * 2;  // two halves of 16 KB, see the descriptors below
 constexpr int kWHalf = kWBytes / 2;
 constexpr int kMaxBatch = 128;
@@ -63,7 +66,7 @@ struct ProjShared {
     alignas(8) uint64_t full[kMaxStagesP], empty[kMaxStagesP];
     uint64_t done;
     uint32_t tmem_base;
-    int dumped;  // the epilogue left this CTA's partial tile in the ring
+    int got[8];  // got[s] = 1: the CTA of input range s has stored its partials here (written by that CTA)
     long long row[kMaxBatch];  // element offset of every sequence's output row (-1: outside the cache), computed once
 };
 
@@ -80,7 +83,8 @@ struct ProjParams {
     const void* bias;                 // [E] added before the activation, or null
     int gelu;                         // x * sigmoid(1.702 x) after the bias (simple-llm/src/gpu/gpu_kernels.py:285-293)
     int stages;
-    int splits;  // CTAs per cluster = ranges of input features per tile
+    int splits;       // CTAs per cluster = ranges of input features per tile: a power of two
+    int split_shift;  // log2(splits)
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -96,17 +100,20 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+// The two halves of a cluster barrier; every thread of every CTA of the cluster executes both, in turn.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Stores a 32-bit word at shared-memory address `local` (an address of this CTA's window) of CTA `rank`.
+__device__ __forceinline__ void peer_store_u32(uint32_t local, uint32_t rank, uint32_t v) {
+    uint32_t addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(local), "r"(rank));
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
-// 32-bit word at the same shared-memory address in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t peer_smem_u32(const void* local, uint32_t rank) {
-    uint32_t addr, v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
-    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
+
+// x * sigmoid(1.702 x), the reference's GELU (simple-llm/src/gpu/gpu_kernels.py:285-293).  The denominator is at
+// least one, so the approximate division (2 ulp, no slow path: sixteen of them run interleaved) is safe; it
+// vanishes in the rounding to bfloat16.
+__device__ __forceinline__ float gelu_sigmoid(float x) { return __fdividef(x, 1.0f + __expf(-1.702f * x)); }
 
 // Instruction descriptor: fp32 accumulate, bf16 operands, A MN-major, B K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t proj_idesc(int n) {
@@ -130,6 +137,9 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
     const uint32_t x_span = static_cast<uint32_t>(p.Bn) * 128u;  // Bn rows of one 64-feature span
     uint8_t* const x_ring = w_ring + p.stages * kWBytes;
     const int n_st = p.stages;
+    // behind the rings when a tile is split: partials of this CTA's sequences, [input range][sequence / splits][feature]
+    float* const recv = reinterpret_cast<float*>(x_ring + p.stages * 2 * x_span);
+    const int rows_per_cta = p.Bn >> p.split_shift;
     const uint32_t stage_bytes = kWBytes + 2 * x_span;
 
     grid_launch_dependents();
@@ -139,10 +149,13 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.done, 1);
-        sm.dumped = 0;
+        for (int s = 0; s < 8; ++s) sm.got[s] = 0;
         fence_mbar_init();
     }
     __syncthreads();  // barriers are initialised: the producer starts while the rest is set up
+    // first cluster barrier: once a CTA has waited for it, all its peers are running with their flags cleared
+    // (the copy warp arrives after its first requests: the arrival orders earlier writes and takes half a microsecond)
+    if (p.splits > 1 && warp != 4) cluster_arrive();
     if (warp == 5) {
         tmem_alloc(&sm.tmem_base, kMaxBatch);
         tmem_relinquish();
@@ -172,27 +185,49 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
         sm.row[b] = row;
     }
 
+    // Split tile: where this CTA's own sequences go and what is added to them is fetched ahead of the sums, eight
+    // sequences at a time: for the first eight while the weights still stream, for the next under the sums.
+    const __nv_bfloat16* const res_split =
+        (p.splits > 1 && p.residual) ? static_cast<const __nv_bfloat16*>(p.residual) + c0 + (threadIdx.x & (kFeat - 1)) : nullptr;
+    float bias_split = 0.f;
+    long long row_next[8];
+    float add_next[8];
+    auto fetch_split = [&](int r0) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int b = ((r0 + u) << p.split_shift) + split;
+            row_next[u] = (r0 + u < rows_per_cta && b < p.B) ? sm.row[b] : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            add_next[u] = (res_split != nullptr && row_next[u] >= 0) ? __bfloat162float(res_split[row_next[u]]) : 0.f;
+    };
+
     if (warp == 4) {
+        const CUtensorMap* tw = which == 0 ? &tm_wq : (which == 1 ? &tm_wk : &tm_wv);
+        // W tile: input features k0 .. +127 (rows), output features c0 .. c0+127 as two 64-wide boxes
+        auto load_w = [&](int st, int k0) {
+            tma_load_2d(w_ring + st * kWBytes, tw, &sm.full[st], c0, k0);
+            tma_load_2d(w_ring + st * kWBytes + kWHalf, tw, &sm.full[st], c0 + 64, k0);
+        };
+        // x tile: every sequence (rows past B read as zero), two 64-feature spans
+        auto load_x = [&](int st, int k0) {
+            tma_load_2d(x_ring + st * 2 * x_span, &tm_x, &sm.full[st], k0, 0);
+            tma_load_2d(x_ring + st * 2 * x_span + x_span, &tm_x, &sm.full[st], k0 + 64, 0);
+        };
+        // the ring starts empty: its first round of weight tiles is on its way before x may be read
+        const int ahead = n_k < n_st ? n_k : n_st;
         if (lane == 0) {
-            const CUtensorMap* tw = which == 0 ? &tm_wq : (which == 1 ? &tm_wk : &tm_wv);
-            // W tile: input features k0 .. +127 (rows), output features c0 .. c0+127 as two 64-wide boxes
-            auto load_w = [&](int st, int k0) {
-                tma_load_2d(w_ring + st * kWBytes, tw, &sm.full[st], c0, k0);
-                tma_load_2d(w_ring + st * kWBytes + kWHalf, tw, &sm.full[st], c0 + 64, k0);
-            };
-            // x tile: every sequence (rows past B read as zero), two 64-feature spans
-            auto load_x = [&](int st, int k0) {
-                tma_load_2d(x_ring + st * 2 * x_span, &tm_x, &sm.full[st], k0, 0);
-                tma_load_2d(x_ring + st * 2 * x_span + x_span, &tm_x, &sm.full[st], k0 + 64, 0);
-            };
-            // the ring starts empty: its first round of weight tiles is on its way before x may be read
-            const int ahead = n_k < n_st ? n_k : n_st;
             for (int i = 0; i < ahead; ++i) {
                 mbar_arrive_expect_tx(&sm.full[i], stage_bytes);
                 load_w(i, (k_first + i) * kKTile);
             }
             grid_dependency_wait();
             for (int i = 0; i < ahead; ++i) load_x(i, (k_first + i) * kKTile);
+        }
+        __syncwarp();
+        if (p.splits > 1) cluster_arrive();
+        if (lane == 0) {
             for (int i = ahead; i < n_k; ++i) {
                 const int st = i % n_st;
                 if (!mbar_wait(&sm.empty[st], ((i / n_st) & 1) ^ 1)) break;
@@ -203,6 +238,7 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             }
         }
         __syncwarp();
+        if (p.splits > 1) cluster_wait();
     } else if (warp == 5) {
         if (lane == 0) {
             tc_fence_after();
@@ -229,40 +265,67 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
             if (ok) mma_commit(&sm.done);
         }
         __syncwarp();
+        if (p.splits > 1) cluster_wait();
     } else {
         // ------------------------------ epilogue: thread = output feature ------------------------------
         const int m = threadIdx.x;  // 0..127, also the TMEM lane
         named_barrier_sync<128>(1);  // sm.row is complete
+        if (p.splits > 1) {
+            cluster_wait();
+            bias_split = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[c0 + m]) : 0.f;
+            fetch_split(0);
+        }
         if (mbar_wait(&sm.done, 0)) {
             tc_fence_after();
             // (the accumulator's address was stored by the issuing warp before its first MMA)
             const uint32_t t_lane = sm.tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-            const int col = c0 + m;  // column inside the weight matrix = element of the output row
-            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which == 0 ? p.q_out : (which == 1 ? p.k_cache : p.v_cache));
-            // inside the row: the element itself for Q, (head, head_dim element) for the cache
-            out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
-            const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
-            const float bias = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : 0.f;
-            float* mine = reinterpret_cast<float*>(w_ring);  // partial tile [Bn][128] fp32 when the tile is split
-            for (int nb = 0; nb < p.Bn; nb += 16) {
-                uint32_t v[16];
-                tmem_ld16(t_lane + nb, v);
-                tmem_wait_ld();
+            if (p.splits > 1) {
+                // sequence b's partial goes to CTA b mod splits, slab `split`, row b / splits
+                const uint32_t mine = smem_u32(recv) + static_cast<uint32_t>((split * rows_per_cta) * kFeat + m) * 4u;
+                for (int nb = 0; nb < p.Bn; nb += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_lane + nb, v);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const long long row = sm.row[nb + j];  // -1 past the batch and for positions outside the cache
-                    if (row < 0) continue;
-                    if (p.splits > 1) {
-                        mine[(nb + j) * kFeat + m] = __uint_as_float(v[j]);
-                    } else {
-                        float acc = __uint_as_float(v[j]) + bias;
-                        if (p.gelu) acc = acc / (1.0f + __expf(-1.702f * acc));
-                        if (res != nullptr) acc += __bfloat162float(res[row]);
-                        out[row] = __float2bfloat16_rn(acc);
+                    for (int j = 0; j < 16; ++j) {
+                        const int b = nb + j;
+                        peer_store_u32(mine + static_cast<uint32_t>((b >> p.split_shift) * kFeat) * 4u,
+                                       static_cast<uint32_t>(b & (p.splits - 1)), v[j]);
                     }
                 }
+                if (m < p.splits) peer_store_u32(smem_u32(&sm.got[split]), static_cast<uint32_t>(m), 1u);
+            } else {
+                const int col = c0 + m;  // column inside the weight matrix = element of the output row
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which == 0 ? p.q_out : (which == 1 ? p.k_cache : p.v_cache));
+                // inside the row: the element itself for Q, (head, head_dim element) for the cache
+                out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
+                const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
+                const float bias = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : 0.f;
+                for (int nb = 0; nb < p.Bn; nb += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_lane + nb, v);
+                    // sixteen sequences at a time, as straight-line code: rows and residuals are fetched together
+                    // (-1: past the batch, or a position outside the cache), then the values, then the stores
+                    long long row[16];
+                    float add[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) row[j] = sm.row[nb + j];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) add[j] = (res != nullptr && row[j] >= 0) ? __bfloat162float(res[row[j]]) : 0.f;
+                    tmem_wait_ld();
+                    __nv_bfloat16 o[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float acc = __uint_as_float(v[j]) + bias;
+                        if (p.gelu) acc = gelu_sigmoid(acc);
+                        if (res != nullptr) acc += add[j];
+                        o[j] = __float2bfloat16_rn(acc);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (row[j] >= 0) out[row[j]] = o[j];
+                }
             }
-            if (m == 0) sm.dumped = 1;
         } else {
             report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
         }
@@ -275,46 +338,40 @@ qkv_append_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_consta
         tmem_dealloc(sm.tmem_base, kMaxBatch);
     }
     if (p.splits > 1) {
-        // every CTA of the tile has its partial in shared memory (or gave up: then nothing is written)
-        cluster_barrier();
+        // second cluster barrier: the partials of this CTA's sequences have arrived (or a CTA gave up and did not
+        // raise its flag: then nothing is written).  Nobody touches a peer's memory after it, so a CTA may leave
+        // as soon as it has written its outputs.
+        cluster_arrive();
+        cluster_wait();
         if (warp < 4) {
             const int m = threadIdx.x;
             bool all = true;
-            for (int sp = 0; sp < p.splits; ++sp) all = all && peer_smem_u32(&sm.dumped, sp) != 0;
+            for (int sp = 0; sp < p.splits; ++sp) all = all && *reinterpret_cast<volatile int*>(&sm.got[sp]) != 0;
             if (all) {
-                const float* mine = reinterpret_cast<const float*>(w_ring);
-                const int col = c0 + m;
-                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(which == 0 ? p.q_out : (which == 1 ? p.k_cache : p.v_cache));
-                out += which == 0 ? col : static_cast<long long>(col / p.D) * p.stride_h + col % p.D;
-                const __nv_bfloat16* res = p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + col : nullptr;
-                const float bias = p.bias ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]) : 0.f;
-                // this CTA's share of the sequences: split, split + splits, ...; eight rows in flight
-                for (int b0 = split; b0 < p.B; b0 += 8 * p.splits) {
-                    float acc[8];
+                // this CTA's sequences: split, split + splits, ...; eight at a time
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.q_out) + c0 + m;  // a split tile is a plain row product
+                for (int r0 = 0; r0 < rows_per_cta; r0 += 8) {
+                    long long row[8];
+                    float add[8], acc[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) acc[u] = bias;
+                    for (int u = 0; u < 8; ++u) row[u] = row_next[u], add[u] = add_next[u], acc[u] = bias_split;
+                    if (r0 + 8 < rows_per_cta) fetch_split(r0 + 8);
                     for (int sp = 0; sp < p.splits; ++sp) {  // fixed order
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const int b = b0 + u * p.splits;
-                            if (b < p.B) acc[u] += __uint_as_float(peer_smem_u32(&mine[b * kFeat + m], sp));
-                        }
+                        for (int u = 0; u < 8; ++u)
+                            if (r0 + u < rows_per_cta) acc[u] += recv[(sp * rows_per_cta + r0 + u) * kFeat + m];
                     }
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
-                        const int b = b0 + u * p.splits;
-                        if (b >= p.B) break;
-                        const long long row = sm.row[b];
-                        if (row < 0) continue;
+                        if (row[u] < 0) continue;
                         float a = acc[u];
-                        if (p.gelu) a = a / (1.0f + __expf(-1.702f * a));
-                        if (res != nullptr) a += __bfloat162float(res[row]);
-                        out[row] = __float2bfloat16_rn(a);
+                        if (p.gelu) a = gelu_sigmoid(a);
+                        if (res_split != nullptr) a += add[u];
+                        out[row[u]] = __float2bfloat16_rn(a);
                     }
                 }
             }
         }
-        cluster_barrier();  // nobody leaves while a peer still reads its shared memory
     }
 }
 
@@ -371,7 +428,7 @@ extern "C" int b2kv_qkv_append(const void* x, const void* wq, const void* wk, co
     const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     proj::ProjParams p{q_out, k_cache, v_cache, seq_pos, dev_status, stride_b, stride_t, stride_h, pos, B, Bn, E, H, D, T_max,
-                       E, nullptr, nullptr, 0, stages, 1};
+                       E, nullptr, nullptr, 0, stages, 1, 0};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;
@@ -392,19 +449,24 @@ extern "C" int b2kv_matmul_rows(const void* x, const void* w, const void* bias, 
     CUtensorMap tw, tx;
     if (!proj::make_matrix_map(&tw, w, K, N, proj::kKTile) || !proj::make_matrix_map(&tx, x, B, K, Bn))
         return B2KV_ERR_UNSUPPORTED;
-    const int stage_bytes = proj::kWBytes + 2 * Bn * 128;
-    const int stages = std::max(2, std::min(proj::kMaxStagesP, proj::kRingBytes / stage_bytes));
-    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024;
     // few tiles: cut the input features so that about 128 CTAs stream (a power of two, at least two stages each)
     const int tiles = N / proj::kFeat, n_k = K / proj::kKTile;
-    int splits = 1;
+    int splits = 1, split_shift = 0;
     if (tune_get("matmul_splits") > 0) {
-        splits = std::min(std::min(tune_get("matmul_splits"), 8), n_k);
+        while (splits * 2 <= std::min(std::min(tune_get("matmul_splits"), 8), n_k)) splits *= 2;
     } else {
         while (splits < 8 && tiles * splits * 2 <= 128 && n_k / (splits * 2) >= 2) splits *= 2;
     }
+    while ((1 << split_shift) < splits) ++split_shift;
+    // a split tile keeps the partials of its own sequences behind the rings: [splits][Bn / splits][128] fp32
+    const int recv_bytes = splits > 1 ? Bn * proj::kFeat * 4 : 0;
+    const int stage_bytes = proj::kWBytes + 2 * Bn * 128;
+    const int ring_bytes = std::min(proj::kRingBytes, proj::kSmemBytes - recv_bytes);
+    const int stages = std::max(2, std::min(proj::kMaxStagesP, ring_bytes / stage_bytes));
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + recv_bytes + 1024;
     // one weight matrix: every tile is of kind 0 (plain rows of `out`); the cache fields are unused
-    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, bias, activation, stages, splits};
+    proj::ProjParams p{out, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, B, Bn, N, 1, N, 1, K, residual, bias, activation,
+                       stages, splits, split_shift};
     int dev = 0;
     B2KV_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return B2KV_ERR_UNSUPPORTED;

@@ -125,9 +125,10 @@ def test_matmul_with_bias_gelu_and_residual_like_the_mlp(pkg, ctx):
     np.testing.assert_allclose(U.to_f32(C), want.astype(np.float32), rtol=RTOL, atol=ATOL)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 5])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 8])
 def test_matmul_rows_with_forced_input_ranges(pkg, ctx, splits):
-    """Every way of cutting the input features over a thread-block cluster gives the same product."""
+    """Every way of cutting the input features over a thread-block cluster gives the same product (the number of
+    ranges is a power of two: 3 is taken as 2, and 8 as 4 because there are only six tiles of input features)."""
     gpu = pkg.gpu
     M, K, N = 16, 768, 256
     A, W, R = _bf16(ctx, (M, K), 31), _bf16(ctx, (K, N), 32, scale=K ** -0.5), _bf16(ctx, (M, N), 33)
