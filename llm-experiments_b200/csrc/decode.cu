@@ -111,9 +111,9 @@ struct DecodeCfg {
     static constexpr int kEpc = Elt<T>::kPerChunk;
     static constexpr int kAcc = kChunksPerLane * kEpc;
     static constexpr int kMergeFloats = NCW * (D + 2);
-    static constexpr int kThreads = (NCW + 1) * 32;
-    static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + (2 * STAGES + 2) * sizeof(uint64_t) +
-                                         STAGES * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 16 + 128;
+    static constexpr int kThreads = (NCW + 2) * 32;  // consumer warps, the copy warp, the merging warp
+    static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + (2 * STAGES + 4) * sizeof(uint64_t) +
+                                         (STAGES + 2) * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 16 + 128;
     static_assert(kRowBytes % 16 == 0, "rows must be whole 16-byte chunks");
     static_assert(kChunksPerRow >= 2, "a row must span at least two lanes");
     static_assert(TILE_T % NCW == 0 && kRowsPerWarp % kRowsPerPass == 0 && kPasses % kBatch == 0, "tile split");
@@ -366,15 +366,14 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES, int NCW>
 __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* stages, uint64_t* full,
-                                                uint64_t* empty, uint64_t* merge_bar, const StageMeta* meta,
-                                                float* merge, const long long* share_size, int* merge_here, int warp,
+                                                uint64_t* empty, uint64_t* hand_full, uint64_t* hand_empty,
+                                                const StageMeta* meta, StageMeta* hand_meta, float* merge, int warp,
                                                 int lane) {
     constexpr int LPR = Cfg::kLanesPerRow;
     constexpr int CPL = Cfg::kChunksPerLane;
     constexpr int EPC = Cfg::kEpc;
     constexpr int NACC = Cfg::kAcc;
     constexpr int RPP = Cfg::kRowsPerPass;
-    constexpr int RPW = Cfg::kRowsPerWarp;
     constexpr int BATCH = Cfg::kBatch;
     const int g = lane / LPR;  // which of the RPP rows of a pass this lane works on
     const int j = lane % LPR;  // which 16-byte chunk(s) of the row
@@ -400,8 +399,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
 
     int stage = 0;
     uint32_t phase = 0;
-    int parity = 0;  // which merge buffer the next finished item uses
-    uint32_t merge_phase = 0;  // phase of merge_bar that the next finished item completes
+    uint32_t item = 0;  // finished items so far: item i is handed over in merge buffer i & 1
 
     while (true) {
         if (!mbar_wait(&full[stage], phase)) {
@@ -409,7 +407,18 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
             return;
         }
         const StageMeta mt = meta[stage];
-        if (mt.flags & kFlagDone) return;
+        if (mt.flags & kFlagDone) {
+            // tell the merging warp that nothing follows (same hand-over as an item)
+            const int buf = item & 1;
+            if (!mbar_wait(&hand_empty[buf], ((item >> 1) & 1u) ^ 1u)) {
+                report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+                return;
+            }
+            if (warp == 0 && lane == 0) hand_meta[buf] = mt;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&hand_full[buf]);
+            return;
+        }
         const uint8_t* Ks = stages + static_cast<size_t>(stage) * Cfg::kStageBytes;
         const uint8_t* Vs = Ks + Cfg::kTileBytes;
 
@@ -428,14 +437,16 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
             }
         }
 
-        const int row0 = warp * RPW;
+        // Rows go to the warps in turn, RPP at a time (pass i of warp w: rows (i * NCW + w) * RPP ...), so that the
+        // few rows of a short tile - the end of a (sequence, head) or of a share - are spread over all the warps.
+        const int row0 = warp * RPP;
         if (row0 < mt.ntok) {
 #pragma unroll 1
             for (int ib = 0; ib < Cfg::kPasses; ib += BATCH) {
                 float s[BATCH];
 #pragma unroll
                 for (int i = 0; i < BATCH; ++i) {
-                    const int r = row0 + (ib + i) * RPP + g;
+                    const int r = row0 + (ib + i) * (NCW * RPP) + g;
                     float part = 0.f;
                     if (r < mt.ntok) {
 #pragma unroll
@@ -458,7 +469,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                 float m_new = m;
 #pragma unroll
                 for (int i = 0; i < BATCH; ++i) {
-                    const int r = row0 + (ib + i) * RPP + g;
+                    const int r = row0 + (ib + i) * (NCW * RPP) + g;
                     if (r >= mt.ntok) s[i] = -INFINITY;
                     m_new = fmaxf(m_new, s[i]);
                 }
@@ -470,7 +481,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                 for (int i = 0; i < NACC; ++i) acc[i] *= corr;
 #pragma unroll
                 for (int i = 0; i < BATCH; ++i) {
-                    const int r = row0 + (ib + i) * RPP + g;
+                    const int r = row0 + (ib + i) * (NCW * RPP) + g;
                     if (r < mt.ntok) {
                         const float pr = exp2f(s[i] - m_use);
                         l += pr;
@@ -514,7 +525,16 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                 }
                 m = m_n;
             }
-            float* mb = merge + parity * Cfg::kMergeFloats + warp * (D + 2);
+            // Hand the warp's partial to the merging warp and go on with the next tile: what follows an item (the
+            // sum over the warps, the store, and for a piece the fence, the ticket and perhaps the merge of all the
+            // pair's pieces: 3 - 4 us of latencies) then costs the stream nothing.  The buffer is free once the
+            // merging warp has read what item - 2 left in it.
+            const int buf = item & 1;
+            if (!mbar_wait(&hand_empty[buf], ((item >> 1) & 1u) ^ 1u)) {
+                report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+                return;
+            }
+            float* mb = merge + buf * Cfg::kMergeFloats + warp * (D + 2);
             if (g == 0) {
 #pragma unroll
                 for (int c = 0; c < CPL; ++c)
@@ -525,123 +545,150 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
                     mb[D + 1] = l;
                 }
             }
-            // The warps meet on an mbarrier, not on a hardware named barrier, so that this wait is bounded
-            // like every other: should a sibling warp have given up on a copy barrier, the others run
-            // out here, report it and leave, instead of waiting for an arrival that never comes.
+            if (warp == 0 && lane == 0) hand_meta[buf] = mt;
             __syncwarp();
-            if (lane == 0) mbar_arrive(merge_bar);
-            if (!mbar_wait(merge_bar, merge_phase)) {
-                report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
-                return;
-            }
-            merge_phase ^= 1u;
-            // all consumer threads: one output column each
-            const float* mr = merge + parity * Cfg::kMergeFloats;
-            float m_all = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < NCW; ++w) m_all = fmaxf(m_all, mr[w * (D + 2) + D]);
-            const float m_u = (m_all == -INFINITY) ? 0.f : m_all;
-            float wgt[NCW];
-            float l_all = 0.f;
-#pragma unroll
-            for (int w = 0; w < NCW; ++w) {
-                wgt[w] = exp2f(mr[w * (D + 2) + D] - m_u);
-                l_all += wgt[w] * mr[w * (D + 2) + D + 1];
-            }
-            const int tid = warp * 32 + lane;
-            if (p.fused_out != nullptr && (mt.flags & kFlagWhole)) {
-                // the whole (sequence, head) was this one item: its row is final
-                // (divided, not multiplied by a reciprocal: bit for bit what the merge kernel gives)
-                T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(mt.slot / p.max_seg) * D;
-                for (int d = tid; d < D; d += NCW * 32) {
-                    float o = 0.f;
-#pragma unroll
-                    for (int w = 0; w < NCW; ++w) o += wgt[w] * mr[w * (D + 2) + d];
-                    orow[d] = Elt<T>::from_float(o / l_all);
-                }
-                parity ^= 1;
-                continue;
-            }
-            for (int d = tid; d < D; d += NCW * 32) {
-                float o = 0.f;
-#pragma unroll
-                for (int w = 0; w < NCW; ++w) o += wgt[w] * mr[w * (D + 2) + d];
-                p.ws_acc[static_cast<size_t>(mt.slot) * D + d] = o;
-            }
-            if (tid == 0) {
-                p.ws_ml[static_cast<size_t>(mt.slot) * 2] = m_all;
-                p.ws_ml[static_cast<size_t>(mt.slot) * 2 + 1] = l_all;
-            }
-            if (p.fused_out != nullptr) {
-                // One piece of several.  Publish it (fence, then the warps meet), take a ticket for the pair: the CTA
-                // that takes the pair's last ticket finds every piece in the workspace and merges them.  Nobody waits
-                // for another CTA.
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(merge_bar);
-                if (!mbar_wait(merge_bar, merge_phase)) {
-                    report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
-                    return;
-                }
-                merge_phase ^= 1u;
-                const int bh = mt.slot / p.max_seg;
-                if (tid == 0) {
-                    unsigned long long* t = p.ws_tickets + bh;
-                    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(t), next;
-                    while (true) {
-                        const unsigned long long assumed = seen;
-                        next = (assumed >> 16) == p.call_id ? assumed + 1ull : ((p.call_id << 16) | 1ull);
-                        seen = atomicCAS(t, assumed, next);
-                        if (seen == assumed) break;
-                    }
-                    *merge_here = (static_cast<int>(next & 0xffffull) == mt.pieces) ? 1 : 0;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(merge_bar);
-                if (!mbar_wait(merge_bar, merge_phase)) {
-                    report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
-                    return;
-                }
-                merge_phase ^= 1u;
-                if (*reinterpret_cast<volatile int*>(merge_here) != 0) {
-                    __threadfence();
-                    const long long size = *share_size;
-                    const long long g_first = mt.pair_off / size, g_last = (mt.pair_off + mt.len - 1) / size;
-                    const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
-                    float m_g = -INFINITY;
-                    for (long long g = g_first; g <= g_last; ++g) {
-                        int t0, t1;
-                        piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
-                        if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[(slot0 + (g - g_first)) * 2]));
-                    }
-                    T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(bh) * D;
-                    for (int d = tid; d < D; d += NCW * 32) {
-                        float l_g = 0.f, o = 0.f;
-                        for (long long g = g_first; g <= g_last; ++g) {
-                            int t0, t1;
-                            piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
-                            if (t0 < t1) {
-                                const size_t sl = slot0 + (g - g_first);
-                                const float wg = exp2f(__ldcg(&p.ws_ml[sl * 2]) - m_g);
-                                l_g += wg * __ldcg(&p.ws_ml[sl * 2 + 1]);
-                                o += wg * __ldcg(&p.ws_acc[sl * D + d]);
-                            }
-                        }
-                        orow[d] = Elt<T>::from_float(o / l_g);
-                    }
-                    // Every piece of the pair has come in, so nobody touches its ticket again in this launch: leave
-                    // it at zero.  A launch replayed from a CUDA graph carries the number it was captured with, and
-                    // must not count on top of its own earlier run.
-                    if (tid == 0) p.ws_tickets[bh] = 0ull;
-                }
-            }
-            parity ^= 1;
+            if (lane == 0) mbar_arrive(&hand_full[buf]);
+            ++item;
         }
     }
 }
 
+// --------------------------------------------------------------------------------------
+// merging warp: finishes the items that the consumer warps hand over
+// --------------------------------------------------------------------------------------
+
+template <typename Cfg, typename T, int D, int TILE_T, int NCW>
+__device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* hand_full, uint64_t* hand_empty,
+                                              const StageMeta* hand_meta, const float* merge,
+                                              const long long* share_size, int lane) {
+    constexpr int CPM = (D + 31) / 32;  // output columns per lane: lane, lane + 32, ...
+    for (uint32_t item = 0;; ++item) {
+        const int buf = item & 1;
+        // Bounded like every wait; it also ends this warp should the consumer warps have given up.
+        if (!mbar_wait(&hand_full[buf], (item >> 1) & 1u)) {
+            report_status(p.dev_status, B2KV_DEV_WAIT_TIMEOUT);
+            return;
+        }
+        const StageMeta mt = hand_meta[buf];
+        if (mt.flags & kFlagDone) return;
+        const float* mr = merge + buf * Cfg::kMergeFloats;
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NCW; ++w) m_all = fmaxf(m_all, mr[w * (D + 2) + D]);
+        const float m_u = (m_all == -INFINITY) ? 0.f : m_all;
+        float wgt[NCW];
+        float l_all = 0.f;
+#pragma unroll
+        for (int w = 0; w < NCW; ++w) {
+            wgt[w] = exp2f(mr[w * (D + 2) + D] - m_u);
+            l_all += wgt[w] * mr[w * (D + 2) + D + 1];
+        }
+        float o[CPM];
+#pragma unroll
+        for (int i = 0; i < CPM; ++i) {
+            const int d = lane + 32 * i;
+            o[i] = 0.f;
+            if (d < D) {
+#pragma unroll
+                for (int w = 0; w < NCW; ++w) o[i] += wgt[w] * mr[w * (D + 2) + d];
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hand_empty[buf]);  // the buffer and its description may be written again
+
+        if (p.fused_out != nullptr && (mt.flags & kFlagWhole)) {
+            // the whole (sequence, head) was this one item: its row is final
+            // (divided, not multiplied by a reciprocal: bit for bit what the merge kernel gives)
+            T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(mt.slot / p.max_seg) * D;
+#pragma unroll
+            for (int i = 0; i < CPM; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) orow[d] = Elt<T>::from_float(o[i] / l_all);
+            }
+            continue;
+        }
+#pragma unroll
+        for (int i = 0; i < CPM; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) p.ws_acc[static_cast<size_t>(mt.slot) * D + d] = o[i];
+        }
+        if (lane == 0) {
+            p.ws_ml[static_cast<size_t>(mt.slot) * 2] = m_all;
+            p.ws_ml[static_cast<size_t>(mt.slot) * 2 + 1] = l_all;
+        }
+        if (p.fused_out == nullptr) continue;  // a merge kernel follows this launch
+        // One piece of several.  Publish it (fence), take a ticket for the pair: the CTA that takes the pair's last
+        // ticket finds every piece in the workspace and merges them.  Nobody waits for another CTA.
+        __threadfence();
+        __syncwarp();
+        const int bh = mt.slot / p.max_seg;
+        int last = 0;
+        if (lane == 0) {
+            unsigned long long* t = p.ws_tickets + bh;
+            unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(t), next;
+            while (true) {
+                const unsigned long long assumed = seen;
+                next = (assumed >> 16) == p.call_id ? assumed + 1ull : ((p.call_id << 16) | 1ull);
+                seen = atomicCAS(t, assumed, next);
+                if (seen == assumed) break;
+            }
+            last = (static_cast<int>(next & 0xffffull) == mt.pieces) ? 1 : 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last == 0) continue;
+        __threadfence();
+        const long long size = *share_size;
+        const long long g_first = mt.pair_off / size, g_last = (mt.pair_off + mt.len - 1) / size;
+        const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
+        // the pieces' common maximum: the lanes share the pieces out
+        float m_g = -INFINITY;
+        for (long long g = g_first + lane; g <= g_last; g += 32) {
+            int t0, t1;
+            piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
+            if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[(slot0 + (g - g_first)) * 2]));
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) m_g = fmaxf(m_g, __shfl_xor_sync(0xffffffffu, m_g, off));
+        // the weighted sums, piece after piece (a fixed order); a lane's columns of a piece are loaded together
+        float l_g = 0.f, og[CPM];
+#pragma unroll
+        for (int i = 0; i < CPM; ++i) og[i] = 0.f;
+        for (long long g = g_first; g <= g_last; ++g) {
+            int t0, t1;
+            piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
+            if (t0 >= t1) continue;
+            const size_t sl = slot0 + (g - g_first);
+            float part[CPM];
+#pragma unroll
+            for (int i = 0; i < CPM; ++i) {
+                const int d = lane + 32 * i;
+                part[i] = d < D ? __ldcg(&p.ws_acc[sl * D + d]) : 0.f;
+            }
+            const float wg = exp2f(__ldcg(&p.ws_ml[sl * 2]) - m_g);
+            l_g += wg * __ldcg(&p.ws_ml[sl * 2 + 1]);
+#pragma unroll
+            for (int i = 0; i < CPM; ++i) og[i] += wg * part[i];
+        }
+        T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(bh) * D;
+#pragma unroll
+        for (int i = 0; i < CPM; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) orow[d] = Elt<T>::from_float(og[i] / l_g);
+        }
+        // Every piece of the pair has come in, so nobody touches its ticket again in this launch: leave
+        // it at zero.  A launch replayed from a CUDA graph carries the number it was captured with, and
+        // must not count on top of its own earlier run.
+        __syncwarp();
+        if (lane == 0) p.ws_tickets[bh] = 0ull;
+    }
+}
+
+// --------------------------------------------------------------------------------------
+// kernel
+// --------------------------------------------------------------------------------------
+
 template <typename T, int D, int TILE_T, int STAGES, int NCW>
-__global__ void __launch_bounds__((NCW + 1) * 32)
+__global__ void __launch_bounds__((NCW + 2) * 32)
 decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v) {
     using Cfg = DecodeCfg<T, D, TILE_T, STAGES, NCW>;
@@ -649,11 +696,13 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint64_t* full = reinterpret_cast<uint64_t*>(stages + static_cast<size_t>(STAGES) * Cfg::kStageBytes);
     uint64_t* empty = full + STAGES;
-    uint64_t* merge_bar = empty + STAGES;  // the consumer warps meet here once per finished item
-    StageMeta* meta = reinterpret_cast<StageMeta*>(empty + STAGES + 2);
-    float* merge = reinterpret_cast<float*>(meta + STAGES);
+    // finished items go from the consumer warps to the merging warp through two buffers
+    uint64_t* hand_full = empty + STAGES;   // [2] the eight warps' partials of an item are in the buffer
+    uint64_t* hand_empty = hand_full + 2;   // [2] the merging warp has read the buffer
+    StageMeta* meta = reinterpret_cast<StageMeta*>(hand_empty + 2);
+    StageMeta* hand_meta = meta + STAGES;   // [2] the item in each buffer
+    float* merge = reinterpret_cast<float*>(hand_meta + 2);
     long long* share_size = reinterpret_cast<long long*>(merge + 2 * Cfg::kMergeFloats);  // tokens per share
-    int* merge_here = reinterpret_cast<int*>(share_size + 1);  // 1: this CTA took the last ticket of the pair in hand
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -661,7 +710,10 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NCW);
         }
-        mbar_init(merge_bar, NCW);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&hand_full[s], NCW);
+            mbar_init(&hand_empty[s], 1);
+        }
         fence_mbar_init();
         // The lengths, the queries and the newest cache rows may come from the kernel before this one.  One thread
         // waits for it and the others sleep at the barrier: a CTA that is launched ahead of time shares its SM
@@ -671,8 +723,11 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     __syncthreads();
     if (warp == NCW) {
         decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, share_size, lane);
+    } else if (warp == NCW + 1) {
+        decode_merger<Cfg, T, D, TILE_T, NCW>(p, hand_full, hand_empty, hand_meta, merge, share_size, lane);
     } else {
-        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, merge_bar, meta, merge, share_size, merge_here, warp, lane);
+        decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, hand_full, hand_empty, meta, hand_meta, merge,
+                                                        warp, lane);
     }
 }
 
