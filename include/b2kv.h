@@ -134,8 +134,10 @@ int b2kv_gather_paged(const void* pool, void* out, const int32_t* seq_lens, int 
  * with n_b = (seq_lens ? seq_lens[b] : len) + len_bias, clamped to [0, T_upper].
  * q, out are [B, H*D].  Sequences with n_b == 0 produce zeros.  The reference's limit of
  * 256 cached tokens (gpu_kv_cache.py:250-257) does not exist here: the cache is
- * processed split-K (flash decoding) and the partial results of a (sequence, head) are merged
- * by the CTA that finishes its last piece.  T_upper is a host-side upper bound of every n_b (at most T_max); it
+ * processed split-K (flash decoding: the caches of all (sequence, head) pairs are cut into chunks,
+ * one large chunk per CTA and small ones that a CTA takes from a counter when it has finished
+ * what it had) and the partial results of a (sequence, head) are merged by the CTA that finishes
+ * its last piece.  T_upper is a host-side upper bound of every n_b (at most T_max); it
  * bounds the lengths read from the device and the size of the launch.  len_bias lets a caller attend over "length after
  * this step's append" without a separate increment of the device lengths.
  * `workspace` is scratch of at least b2kv_decode_workspace_bytes(...) bytes; it needs no
@@ -208,12 +210,13 @@ int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* ou
  * Limits and rules:
  *   - Shapes whose partials do not fit are refused with B2KV_ERR_STATIC_LIMIT before anything is
  *     launched; use b2kv_decode with your own workspace for those.  The partials take
- *     B * H * (ceil(CTAs / H) + 2) slots of (D + 2) * 4 bytes (plus 8 bytes per (sequence, head)
- *     for the tickets), where CTAs is the persistent grid:
+ *     2 * (10 * CTAs + 2) + B * H slots of (D + 2) * 4 bytes (two per chunk of work that the
+ *     launch may cut the caches into, one per (sequence, head)), plus 8 bytes per (sequence,
+ *     head) for the tickets and 8 for the chunk counter, where CTAs is the persistent grid:
  *     the SM count times the resident CTAs per SM of the compiled variant (three for 256-byte
  *     rows, at most four for any row size), and never more than the tiles of work.  The
- *     benchmark shape (B=64, H=32, D=128, bf16; 444 CTAs on a 148-SM B200) needs 32768 slots
- *     = 17.0 MB and fits; B=128 with the same heads does not.
+ *     benchmark shape (B=64, H=32, D=128, bf16; 444 CTAs on a 148-SM B200) needs 10932 slots
+ *     = 5.7 MB and fits; B=4096 with the same heads does not.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call before starting
  *     any stream capture on that device.
@@ -363,7 +366,8 @@ int b2kv_matmul(const void* a, const void* w, const void* bias, const void* resi
 /*
  * Tuning hook for experiments (process-global and unsynchronised: set knobs before launching work, never while
  * another thread is inside a b2kv call): sets an integer knob by name ("decode_variant",
- * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map",
+ * "decode_grid_per_sm", "decode_l2_keep", "decode_no_tensor_map", "decode_dynamic_chunks": small chunks of the
+ * decode's work handed out on demand, 0 = for long launches only, 1 = always, 2 = never,
  * "prefill_force_simt", "prefill_variant": 2 = CTA-pair prefill kernel for bf16, D = 128,
  * N a multiple of 256, "prefill_f32_simt": 1 = b2kv_prefill_ws never takes the
  * split-bfloat16 tensor-core kernel, "prefill_unfused_paged": 1 = b2kv_prefill_paged always

@@ -34,6 +34,7 @@ static Knob g_knobs[] = {
     {"prefill_test_expire", 0},  // test hook: 1 = the softmax warps of the one-CTA tensor-core prefill give up at once
     {"prefill_group", 0},  // one-CTA tensor-core prefill: (sequence, head) pairs per launch group; 0 = by size, -1 = all
     {"matmul_splits", 0},  // ranges of input features per tile in b2kv_matmul_rows (0 = by shape)
+    {"decode_dynamic_chunks", 0},  // small chunks of the decode's token space handed out on demand: 0 = by size, 1 = always, 2 = never
     {"serial_launches", 0},  // 1 = no kernel is launched ahead of the end of the kernel before it (plain stream order)
     {"gemm_variant", 0},   // b2kv_matmul: 0 = by shape and device, 1 = one CTA per tile, 2 / 3 = CTA pairs, 64 / 128 features per stage
 };

@@ -45,7 +45,7 @@ struct StageMeta {
     int pieces;          // pieces with tokens that the item's (sequence, head) was cut into, over all CTAs
     long long pair_off;  // where the (sequence, head) starts in the token space
     int len;             // its length
-    int pad;
+    int bh;              // sequence * H + head
 };
 
 // Optional epilogue of the merge kernel: instead of writing its row to a local output, every
@@ -72,7 +72,7 @@ struct DecodeParams {
     int32_t* dev_status;
     int len_scalar, len_bias;
     int B, H, T_upper;
-    int max_seg;  // partial-result slots per (sequence, head): the most CTA shares one can overlap
+    int n_slots;  // partial-result slots in the workspace: two per chunk of the token space
     int max_blocks, block_size, n_blocks;
     int run_len;  // tokens that one bulk copy may cover (contiguous in memory)
     int l2_evict_first;  // 1: K/V copies carry the evict-first L2 policy (each row is read once)
@@ -88,12 +88,25 @@ struct DecodeParams {
     unsigned long long* ws_tickets;  // [B*H]: (call number << 16) | pieces of the pair finished in that call
     unsigned long long call_id;      // unique per launch call, 48 bits, never 0: tickets left by other calls never count
                                      // (a finished pair's ticket goes back to 0, for launches replayed from a graph)
+    int dynamic_chunks;              // 0: by the size of the batch, 1: always, 2: never hand out small chunks on demand
+    unsigned long long* ws_counter;  // (low 40 bits of the call number << 24) | chunks handed out so far in that call;
+                                     // back to 0 when the last CTA has asked
 };
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
     int n = (p.seq_lens ? p.seq_lens[b] : p.len_scalar) + p.len_bias;
     return min(max(n, 0), p.T_upper);
 }
+
+// How a launch cuts the batch's token space into chunks (see "work split" below).
+struct Geometry {
+    long long total;  // tokens in the token space
+    long long sa;     // tokens per advance chunk (a multiple of the tile)
+    long long a_end;  // where the small chunks begin: min(n_static * sa, total)
+    long long sb;     // tokens per small chunk (a multiple of the tile)
+    int n_static;     // advance chunks = CTAs
+    int n_chunks;     // n_static + small chunks
+};
 
 template <typename T, int D, int TILE_T, int STAGES, int NCW>
 struct DecodeCfg {
@@ -113,36 +126,78 @@ struct DecodeCfg {
     static constexpr int kMergeFloats = NCW * (D + 2);
     static constexpr int kThreads = (NCW + 2) * 32;  // consumer warps, the copy warp, the merging warp
     static constexpr size_t kSmemBytes = static_cast<size_t>(STAGES) * kStageBytes + (2 * STAGES + 4) * sizeof(uint64_t) +
-                                         (STAGES + 2) * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + 16 + 128;
+                                         (STAGES + 2) * sizeof(StageMeta) + 2 * kMergeFloats * sizeof(float) + sizeof(Geometry) + 8 + 128;
+    // CTAs that the shared memory of an SM holds, three at most: the register budget is set to let them in
+    static constexpr int kCtasPerSm = (232448 / (kSmemBytes + 1024)) < 1 ? 1 : ((232448 / (kSmemBytes + 1024)) > 3 ? 3 : static_cast<int>(232448 / (kSmemBytes + 1024)));
     static_assert(kRowBytes % 16 == 0, "rows must be whole 16-byte chunks");
     static_assert(kChunksPerRow >= 2, "a row must span at least two lanes");
     static_assert(TILE_T % NCW == 0 && kRowsPerWarp % kRowsPerPass == 0 && kPasses % kBatch == 0, "tile split");
 };
 
 // --------------------------------------------------------------------------------------
-// work split: one contiguous share of the batch's token space per CTA
+// work split: chunks of the batch's token space, one large one per CTA and small ones on demand
 // --------------------------------------------------------------------------------------
+//
+// The caches of all (sequence, head) pairs laid end to end are one token space of H * sum_b n_b tokens.
+// CTAs that share an SM, and SMs among themselves, do not stream at the same rate (finishing times of equal
+// shares were measured 8 % either side of their mean), so equal shares leave most of the machine idle at the
+// end.  The first three quarters of the space are therefore dealt out as one chunk per CTA (chunk g = CTA g),
+// and the rest as small chunks (a thirty-second of a CTA's equal share) that a CTA takes from a counter when
+// it has finished what it had.  Chunk numbers grow with the position in the token space.  Every cut adds a
+// piece that has to be merged, so a launch whose equal shares are short (less than 256 tiles: there small chunks
+// were measured to cost more than they even out, 227 against 170 us at 79 tiles per CTA) is dealt out whole, as
+// equal shares.  Interleaved runs at 319 tiles per CTA: 675 us against 695 us for equal shares (long run,
+// power-capped clocks).
 
-struct Share {
-    long long start, end;  // this CTA's range of the token space [0, H * sum_b n_b)
-    long long size;        // tokens per share (a multiple of the tile, the same for every CTA)
-};
+constexpr int kStaticNum = 3, kStaticDen = 4;  // part of the token space dealt out in advance
+constexpr int kChunksPerShare = 32;            // small chunks that an equal share would be cut into
+constexpr int kMinChunkTiles = 8;              // a small chunk lasts long enough for the merging warp to keep up
+constexpr int kMinDynamicTiles = 256;          // equal shares shorter than this many tiles are dealt out whole
+
+// Most chunks of any batch for a grid of `n_ctas` (the small part is at most a quarter of the space plus what
+// rounding adds, a small chunk at least a thirty-second of an equal share).
+__host__ __device__ constexpr int max_chunks(int n_ctas) { return n_ctas * (2 + kChunksPerShare * (kStaticDen - kStaticNum) / kStaticDen) + 2; }
 
 // Every thread of the calling warp takes part (the lengths are summed across the lanes).
-__device__ __forceinline__ Share share_of(const DecodeParams& p, int cta, int n_ctas, int tile, int lane) {
+__device__ __forceinline__ Geometry geometry_of(const DecodeParams& p, int n_ctas, int tile, int lane) {
     long long sum = 0;
     for (int b = lane; b < p.B; b += 32) sum += seq_len_of(p, b);
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    const long long total = sum * p.H;
-    long long size = (total + n_ctas - 1) / n_ctas;
-    size = (size + tile - 1) / tile * tile;
-    if (size < tile) size = tile;
-    Share s;
-    s.size = size;
-    s.start = min(static_cast<long long>(cta) * size, total);
-    s.end = min(s.start + size, total);
-    return s;
+    Geometry ge;
+    ge.total = sum * p.H;
+    const long long per = (ge.total + n_ctas - 1) / n_ctas;  // an equal share
+    // a short launch is dealt out whole: the small chunks' extra pieces and requests cost more than they even out
+    const bool on_demand = p.dynamic_chunks == 1 || (p.dynamic_chunks == 0 && per >= static_cast<long long>(kMinDynamicTiles) * tile);
+    ge.sa = ((on_demand ? (per * kStaticNum + kStaticDen - 1) / kStaticDen : per) + tile - 1) / tile * tile;
+    if (ge.sa < tile) ge.sa = tile;
+    ge.sb = ((per + kChunksPerShare - 1) / kChunksPerShare + tile - 1) / tile * tile;
+    if (ge.sb < static_cast<long long>(kMinChunkTiles) * tile) ge.sb = static_cast<long long>(kMinChunkTiles) * tile;
+    ge.n_static = n_ctas;
+    ge.a_end = min(static_cast<long long>(n_ctas) * ge.sa, ge.total);
+    ge.n_chunks = n_ctas + static_cast<int>((ge.total - ge.a_end + ge.sb - 1) / ge.sb);
+    return ge;
+}
+
+__device__ __forceinline__ void chunk_range(const Geometry& ge, long long g, long long& start, long long& end) {
+    if (g < ge.n_static) {
+        start = min(g * ge.sa, ge.a_end);
+        end = min(start + ge.sa, ge.a_end);
+    } else {
+        start = min(ge.a_end + (g - ge.n_static) * ge.sb, ge.total);
+        end = min(start + ge.sb, ge.total);
+    }
+}
+
+// The chunk that holds position `pos` (< total) of the token space.
+__device__ __forceinline__ long long chunk_of(const Geometry& ge, long long pos) {
+    return pos < ge.a_end ? pos / ge.sa : ge.n_static + (pos - ge.a_end) / ge.sb;
+}
+
+// Where the piece of a (sequence, head) inside chunk g leaves its partial result: a chunk holds at most two
+// pieces of pairs that other chunks share, the pair that began before the chunk and the pair that goes on after it.
+__device__ __forceinline__ int piece_slot(long long g, long long chunk_start, long long pair_off) {
+    return static_cast<int>(2 * g + (pair_off >= chunk_start ? 1 : 0));
 }
 
 // The piece [t_begin, t_end) of a (sequence, head) of `len` tokens at `pair_off` in the token
@@ -185,6 +240,26 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
     }
 }
 
+// Takes the next small chunk from the launch's counter (a number past the last chunk: none is left).  The counter
+// word carries the launch's number above its count, so that whatever another launch or an uninitialised workspace
+// left there never counts: the first CTAs to arrive put the launch's number in (one compare-and-swap each; a CTA
+// that loses sees the number and goes on), everybody then counts with a plain atomic add, which needs no retries
+// however many CTAs ask at once.
+__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge) {
+    const unsigned long long tag = (p.call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
+    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(p.ws_counter);
+    while ((seen & ~0xffffffull) != tag) {
+        const unsigned long long old = atomicCAS(p.ws_counter, seen, tag);
+        if (old == seen) break;
+        seen = old;
+    }
+    const long long asked = static_cast<long long>(atomicAdd(p.ws_counter, 1ull) & 0xffffffull) + 1;  // this request included
+    // Every CTA asks until it is turned away: small chunks + CTAs requests in all.  The last one leaves a zero (a
+    // launch replayed from a CUDA graph carries the number it was captured with and must not count on).
+    if (asked == static_cast<long long>(ge.n_chunks - ge.n_static) + ge.n_static) *p.ws_counter = 0ull;
+    return ge.n_static + asked - 1;
+}
+
 // --------------------------------------------------------------------------------------
 // producer warp
 // --------------------------------------------------------------------------------------
@@ -192,7 +267,7 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
 template <typename Cfg, typename T, int D, int TILE_T, int STAGES>
 __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUtensorMap* tm_k,
                                                 const CUtensorMap* tm_v, uint8_t* stages, uint64_t* full,
-                                                uint64_t* empty, StageMeta* meta, long long* share_size, int lane) {
+                                                uint64_t* empty, StageMeta* meta, Geometry* geo, int lane) {
     const char* kbase = static_cast<const char*>(p.k);
     const char* vbase = static_cast<const char*>(p.v);
     const char* qbase = static_cast<const char*>(p.q);
@@ -200,55 +275,61 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
     uint32_t phase = 0;
     long long fills = 0;  // stages filled so far (for the drain after a failed wait)
     bool ok = true;
-    bool let_go = false;  // grid_launch_dependents() has been executed
-    constexpr int kLetGoTiles = 8;
 
     const uint64_t l2_policy = l2_policy_evict_first();
-    const Share sh = share_of(p, blockIdx.x, gridDim.x, TILE_T, lane);
-    if (lane == 0) *share_size = sh.size;  // (published to the consumers with the first stage's barrier)
-    // first (sequence, head) that the share touches
+    const Geometry ge = geometry_of(p, gridDim.x, TILE_T, lane);
+    if (lane == 0) *geo = ge;  // (published to the other warps with the first stage's barrier)
+    const bool on_demand = ge.n_chunks > ge.n_static;
+
+    // this CTA's chunks: its own advance chunk, then small ones as long as the counter has some
+    for (long long chunk = blockIdx.x; ok && chunk < ge.n_chunks;) {
+    long long c_start, c_end;
+    chunk_range(ge, chunk, c_start, c_end);
+    // Ask for the chunk after this one now.  Every CTA asks until it is turned away, so the launch's last request
+    // is known by its number and puts the counter back to zero (for a launch replayed from a CUDA graph).
+    long long chunk_next = ge.n_chunks;
+    if (on_demand) {
+        if (lane == 0) chunk_next = claim_chunk(p, ge);
+        chunk_next = __shfl_sync(0xffffffffu, chunk_next, 0);
+    }
+    // first (sequence, head) that the chunk touches
     int b = p.B;
     long long tok_before = 0;  // tokens of the sequences that precede b
     int len_b = 0;
-    if (sh.start < sh.end) locate_sequence(p, sh.start, lane, b, tok_before, len_b);
-    int h = (b < p.B) ? static_cast<int>((sh.start - tok_before * p.H) / len_b) : 0;
+    if (c_start < c_end) locate_sequence(p, c_start, lane, b, tok_before, len_b);
+    int h = (b < p.B) ? static_cast<int>((c_start - tok_before * p.H) / len_b) : 0;
 
     while (ok && b < p.B) {
         const long long pair_off = tok_before * p.H + static_cast<long long>(h) * len_b;
-        if (pair_off >= sh.end) break;
+        if (pair_off >= c_end) break;
         int t_begin, t_end;
-        piece_of(sh.start, sh.end, pair_off, len_b, TILE_T, t_begin, t_end);
-        const long long seg = static_cast<long long>(blockIdx.x) - pair_off / sh.size;
-        if (t_begin < t_end && (seg < 0 || seg >= p.max_seg)) {
-            report_status(p.dev_status, B2KV_DEV_BAD_POSITION);  // cannot happen: sized on the host
-            t_end = t_begin;
-        }
-        const int slot = (b * p.H + h) * p.max_seg + static_cast<int>(seg);
-        // how many CTAs hold a piece with tokens of this pair (the merge inside this kernel counts them in)
-        int pieces = 1;
-        if (p.fused_out != nullptr) {
-            const long long g_first = pair_off / sh.size, g_last = (pair_off + len_b - 1) / sh.size;
-            int cnt = 0;
+        piece_of(c_start, c_end, pair_off, len_b, TILE_T, t_begin, t_end);
+        // how many chunks hold a piece with tokens of this pair (the merge counts them in)
+        int pieces = 0;
+        {
+            const long long g_first = chunk_of(ge, pair_off), g_last = chunk_of(ge, pair_off + len_b - 1);
             for (long long g = g_first + lane; g <= g_last; g += 32) {
+                long long s0, s1;
+                chunk_range(ge, g, s0, s1);
                 int t0, t1;
-                piece_of(g * sh.size, (g + 1) * sh.size, pair_off, len_b, TILE_T, t0, t1);
-                cnt += (t0 < t1) ? 1 : 0;
+                piece_of(s0, s1, pair_off, len_b, TILE_T, t0, t1);
+                pieces += (t0 < t1) ? 1 : 0;
             }
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
-            pieces = cnt;
+            for (int off = 16; off >= 1; off >>= 1) pieces += __shfl_xor_sync(0xffffffffu, pieces, off);
+        }
+        // a pair in one piece has a slot of its own (used when a merge kernel follows), a piece of several is one
+        // of its chunk's two
+        const int bh = b * p.H + h;
+        int slot = pieces == 1 ? p.n_slots - p.B * p.H + bh : piece_slot(chunk, c_start, pair_off);
+        if (t_begin < t_end && (slot < 0 || slot >= p.n_slots)) {
+            report_status(p.dev_status, B2KV_DEV_BAD_POSITION);  // cannot happen: sized on the host
+            t_end = t_begin;
+            slot = 0;
         }
 
         for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
             const int ntok = min(TILE_T, t_end - t0);
-            // A few tiles before the end of the share the next kernel in the stream may be scheduled (it waits
-            // for the end of this grid before it reads or writes anything): its launch then costs no time between
-            // the two.  Not earlier: CTAs that wait next to streaming ones for the whole launch were measured to
-            // slow those down (the step went from 0.67 to 0.82 ms).
-            if (!let_go && sh.end - (pair_off + t0) <= kLetGoTiles * TILE_T) {
-                grid_launch_dependents();
-                let_go = true;
-            }
             // paged: this lane's block of the tile is looked up before the wait for a free stage, so that the table's
             // latency falls into that wait and not between a stage coming free and its copies going out
             int blk_ahead = -1;
@@ -270,7 +351,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
                 mt.pieces = pieces;
                 mt.pair_off = pair_off;
                 mt.len = len_b;
-                mt.pad = 0;
+                mt.bh = bh;
                 meta[stage] = mt;
                 // a tiled load always delivers the whole box (rows past the end arrive as zeros or as
                 // the next rows of the cache; the consumers use the first ntok only)
@@ -336,8 +417,9 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
             } while (b < p.B && len_b == 0);
         }
     }
+    chunk = chunk_next;
+    }
 
-    if (!let_go) grid_launch_dependents();
     if (ok && mbar_wait(&empty[stage], phase ^ 1u)) {
         if (lane == 0) {
             StageMeta mt;
@@ -347,7 +429,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
             mt.pieces = 0;
             mt.pair_off = 0;
             mt.len = 0;
-            mt.pad = 0;
+            mt.bh = 0;
             meta[stage] = mt;
             mbar_arrive(&full[stage]);
         }
@@ -560,7 +642,7 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
 template <typename Cfg, typename T, int D, int TILE_T, int NCW>
 __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* hand_full, uint64_t* hand_empty,
                                               const StageMeta* hand_meta, const float* merge,
-                                              const long long* share_size, int lane) {
+                                              const Geometry* geo, int lane) {
     constexpr int CPM = (D + 31) / 32;  // output columns per lane: lane, lane + 32, ...
     for (uint32_t item = 0;; ++item) {
         const int buf = item & 1;
@@ -599,7 +681,7 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         if (p.fused_out != nullptr && (mt.flags & kFlagWhole)) {
             // the whole (sequence, head) was this one item: its row is final
             // (divided, not multiplied by a reciprocal: bit for bit what the merge kernel gives)
-            T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(mt.slot / p.max_seg) * D;
+            T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(mt.bh) * D;
 #pragma unroll
             for (int i = 0; i < CPM; ++i) {
                 const int d = lane + 32 * i;
@@ -621,7 +703,7 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         // ticket finds every piece in the workspace and merges them.  Nobody waits for another CTA.
         __threadfence();
         __syncwarp();
-        const int bh = mt.slot / p.max_seg;
+        const int bh = mt.bh;
         int last = 0;
         if (lane == 0) {
             unsigned long long* t = p.ws_tickets + bh;
@@ -637,15 +719,16 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last == 0) continue;
         __threadfence();
-        const long long size = *share_size;
-        const long long g_first = mt.pair_off / size, g_last = (mt.pair_off + mt.len - 1) / size;
-        const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
-        // the pieces' common maximum: the lanes share the pieces out
+        const Geometry ge = *geo;
+        const long long g_first = chunk_of(ge, mt.pair_off), g_last = chunk_of(ge, mt.pair_off + mt.len - 1);
+        // the pieces' common maximum: the lanes share the chunks out
         float m_g = -INFINITY;
         for (long long g = g_first + lane; g <= g_last; g += 32) {
+            long long s0, s1;
+            chunk_range(ge, g, s0, s1);
             int t0, t1;
-            piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
-            if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[(slot0 + (g - g_first)) * 2]));
+            piece_of(s0, s1, mt.pair_off, mt.len, TILE_T, t0, t1);
+            if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[static_cast<size_t>(piece_slot(g, s0, mt.pair_off)) * 2]));
         }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) m_g = fmaxf(m_g, __shfl_xor_sync(0xffffffffu, m_g, off));
@@ -654,10 +737,12 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
 #pragma unroll
         for (int i = 0; i < CPM; ++i) og[i] = 0.f;
         for (long long g = g_first; g <= g_last; ++g) {
+            long long s0, s1;
+            chunk_range(ge, g, s0, s1);
             int t0, t1;
-            piece_of(g * size, (g + 1) * size, mt.pair_off, mt.len, TILE_T, t0, t1);
+            piece_of(s0, s1, mt.pair_off, mt.len, TILE_T, t0, t1);
             if (t0 >= t1) continue;
-            const size_t sl = slot0 + (g - g_first);
+            const size_t sl = static_cast<size_t>(piece_slot(g, s0, mt.pair_off));
             float part[CPM];
 #pragma unroll
             for (int i = 0; i < CPM; ++i) {
@@ -688,7 +773,7 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
 // --------------------------------------------------------------------------------------
 
 template <typename T, int D, int TILE_T, int STAGES, int NCW>
-__global__ void __launch_bounds__((NCW + 2) * 32)
+__global__ void __launch_bounds__((NCW + 2) * 32, DecodeCfg<T, D, TILE_T, STAGES, NCW>::kCtasPerSm)
 decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v) {
     using Cfg = DecodeCfg<T, D, TILE_T, STAGES, NCW>;
@@ -702,7 +787,7 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     StageMeta* meta = reinterpret_cast<StageMeta*>(hand_empty + 2);
     StageMeta* hand_meta = meta + STAGES;   // [2] the item in each buffer
     float* merge = reinterpret_cast<float*>(hand_meta + 2);
-    long long* share_size = reinterpret_cast<long long*>(merge + 2 * Cfg::kMergeFloats);  // tokens per share
+    Geometry* geo = reinterpret_cast<Geometry*>(merge + 2 * Cfg::kMergeFloats);  // how the token space is cut
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -722,9 +807,9 @@ decode_split_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
     }
     __syncthreads();
     if (warp == NCW) {
-        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, share_size, lane);
+        decode_producer<Cfg, T, D, TILE_T, STAGES>(p, &tm_k, &tm_v, stages, full, empty, meta, geo, lane);
     } else if (warp == NCW + 1) {
-        decode_merger<Cfg, T, D, TILE_T, NCW>(p, hand_full, hand_empty, hand_meta, merge, share_size, lane);
+        decode_merger<Cfg, T, D, TILE_T, NCW>(p, hand_full, hand_empty, hand_meta, merge, geo, lane);
     } else {
         decode_consumer<Cfg, T, D, TILE_T, STAGES, NCW>(p, stages, full, empty, hand_full, hand_empty, meta, hand_meta, merge,
                                                         warp, lane);
@@ -737,40 +822,53 @@ template <typename T, int D>
 __global__ void __launch_bounds__(D < 32 ? 32 : D) decode_combine_kernel(const DecodeParams p, T* __restrict__ out,
                                                                        int n_ctas, int tile) {
     __shared__ long long sh_before;
-    __shared__ Share sh_share;
+    __shared__ Geometry sh_geo;
     const int bh = blockIdx.x;
     const int b = bh / p.H, h = bh - b * p.H;
     const int d = threadIdx.x;
     if (threadIdx.x < 32) {
-        const Share s0 = share_of(p, 0, n_ctas, tile, threadIdx.x);
+        const Geometry ge = geometry_of(p, n_ctas, tile, threadIdx.x);
         long long before = 0;
         for (int i = threadIdx.x; i < b; i += 32) before += seq_len_of(p, i);
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) before += __shfl_xor_sync(0xffffffffu, before, off);
         if (threadIdx.x == 0) {
             sh_before = before;
-            sh_share = s0;
+            sh_geo = ge;
         }
     }
     __syncthreads();
     const int n = seq_len_of(p, b);
     float m_all = -INFINITY, l_all = 0.f, o = 0.f;
     if (d < D && n > 0) {
-        const long long size = sh_share.size;
+        const Geometry ge = sh_geo;
         const long long pair_off = sh_before * p.H + static_cast<long long>(h) * n;
-        const long long g_first = pair_off / size, g_last = (pair_off + n - 1) / size;
-        const size_t slot0 = static_cast<size_t>(bh) * p.max_seg;
-        // first pass: the common maximum; second pass: the weighted sums
+        const long long g_first = chunk_of(ge, pair_off), g_last = chunk_of(ge, pair_off + n - 1);
+        // first pass: the pieces and their common maximum; second pass: the weighted sums.  A pair in one piece
+        // has a slot of its own, a piece of several is one of its chunk's two.
+        int pieces = 0;
         for (long long g = g_first; g <= g_last; ++g) {
+            long long s0, s1;
+            chunk_range(ge, g, s0, s1);
             int t0, t1;
-            piece_of(g * size, (g + 1) * size, pair_off, n, tile, t0, t1);
-            if (t0 < t1) m_all = fmaxf(m_all, p.ws_ml[(slot0 + (g - g_first)) * 2]);
+            piece_of(s0, s1, pair_off, n, tile, t0, t1);
+            pieces += (t0 < t1) ? 1 : 0;
+        }
+        const size_t own = static_cast<size_t>(p.n_slots - p.B * p.H + bh);
+        for (long long g = g_first; g <= g_last; ++g) {
+            long long s0, s1;
+            chunk_range(ge, g, s0, s1);
+            int t0, t1;
+            piece_of(s0, s1, pair_off, n, tile, t0, t1);
+            if (t0 < t1) m_all = fmaxf(m_all, p.ws_ml[(pieces == 1 ? own : static_cast<size_t>(piece_slot(g, s0, pair_off))) * 2]);
         }
         for (long long g = g_first; g <= g_last; ++g) {
+            long long s0, s1;
+            chunk_range(ge, g, s0, s1);
             int t0, t1;
-            piece_of(g * size, (g + 1) * size, pair_off, n, tile, t0, t1);
+            piece_of(s0, s1, pair_off, n, tile, t0, t1);
             if (t0 < t1) {
-                const size_t slot = slot0 + (g - g_first);
+                const size_t slot = pieces == 1 ? own : static_cast<size_t>(piece_slot(g, s0, pair_off));
                 const float wgt = exp2f(p.ws_ml[slot * 2] - m_all);
                 l_all += wgt * p.ws_ml[slot * 2 + 1];
                 o += wgt * p.ws_acc[slot * D + d];
@@ -845,9 +943,11 @@ constexpr int default_tile(int row_bytes) {
 // Most CTAs per SM that a launch uses: the grid is persistent, more would only add partials.
 constexpr int kMaxCtasPerSm = 4;
 
-// Partial-result slots per (sequence, head) for a grid of `n_ctas`: a pair of n tokens overlaps at
-// most n / share + 2 shares, and n / share <= n_ctas / H because share >= H * sum(n_b) / n_ctas >= H * n / n_ctas.
-static int max_segments(int n_ctas, int H) { return (n_ctas + H - 1) / H + 2; }
+// Partial-result slots for a grid of `n_ctas`: two per chunk (a chunk shares at most its first and its last
+// (sequence, head) with other chunks) and one per (sequence, head) for pairs in one piece.
+static size_t partial_slots(int n_ctas, int B, int H) {
+    return 2 * static_cast<size_t>(max_chunks(n_ctas)) + static_cast<size_t>(B) * H;
+}
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -887,8 +987,11 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     const long long tiles_upper = static_cast<long long>(p.B) * p.H * ((p.T_upper + TILE_T - 1) / TILE_T);
     int grid = static_cast<int>(tiles_upper < grid_full ? tiles_upper : grid_full);
     if (grid < 1) grid = 1;
-    p.max_seg = max_segments(grid, p.H);
+    const size_t slots = partial_slots(grid, p.B, p.H);
+    if (slots > 0x7fffffffull) return B2KV_ERR_UNSUPPORTED;
+    p.n_slots = static_cast<int>(slots);
     p.l2_evict_first = tune_get("decode_l2_keep") ? 0 : 1;
+    p.dynamic_chunks = tune_get("decode_dynamic_chunks");
 
     // a bulk copy may cover several rows only when rows are adjacent in memory
     if (p.stride_t == D) {
@@ -899,14 +1002,15 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
         p.run_len = 1;
     }
 
-    const size_t slots = static_cast<size_t>(p.B) * p.H * p.max_seg;
     const size_t acc_bytes = align_up(slots * D * sizeof(float), 256);
     const size_t ml_bytes = align_up(slots * 2 * sizeof(float), 8);
-    const size_t need = acc_bytes + ml_bytes + static_cast<size_t>(p.B) * p.H * sizeof(unsigned long long);
+    const size_t ticket_bytes = static_cast<size_t>(p.B) * p.H * sizeof(unsigned long long);
+    const size_t need = acc_bytes + ml_bytes + ticket_bytes + sizeof(unsigned long long);
     if (workspace == nullptr || workspace_bytes < need) return B2KV_ERR_WORKSPACE;
     p.ws_acc = static_cast<float*>(workspace);
     p.ws_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
     p.ws_tickets = reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + acc_bytes + ml_bytes);
+    p.ws_counter = p.ws_tickets + static_cast<size_t>(p.B) * p.H;
     // The plain decode merges inside the split kernel; the forms whose merge has more to do (peer stores of the
     // fused all-gather, unnormalised partials of the sequence split) keep the merge kernel.
     const bool fused_merge = p.gather.peer_out == nullptr && p.partial_out == nullptr && !tune_get("decode_merge_kernel");
@@ -1049,9 +1153,9 @@ size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype) 
     if (B <= 0 || H <= 0 || D <= 0 || T_upper <= 0 || es == 0 || (D * es) % 16 != 0) return 0;
     // An upper bound of what any compiled variant will ask for: the largest grid a launch uses.
     (void)T_upper;
-    const size_t slots = static_cast<size_t>(B) * H * max_segments(device_sm_count() * kMaxCtasPerSm, H);
+    const size_t slots = partial_slots(device_sm_count() * kMaxCtasPerSm, B, H);
     return align_up(slots * D * sizeof(float), 256) + align_up(slots * 2 * sizeof(float), 8) +
-           static_cast<size_t>(B) * H * sizeof(unsigned long long) + 256;
+           static_cast<size_t>(B) * H * sizeof(unsigned long long) + sizeof(unsigned long long) + 256;
 }
 
 int b2kv_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens, int len,

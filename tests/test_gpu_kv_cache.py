@@ -400,3 +400,85 @@ def test_decode_replayed_from_a_cuda_graph(pkg, ctx):
         v4 = cache.layers[0].v_cache.buffer.view(B, H, T, D).permute(0, 2, 1, 3)
         want = U.oracle_decode(q, k4.contiguous(), v4.contiguous(), lens)
         np.testing.assert_allclose(U.to_f32(replayed), want, **U.TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype,layout,block_size,B,H,D,T,merge_kernel", [
+    (torch.bfloat16, "bhtd", 0, 6, 8, 128, 9000, 0),    # several chunks per CTA, pairs cut into many pieces
+    (torch.bfloat16, "bhtd", 0, 6, 8, 128, 9000, 1),    # the same through the separate merge kernel
+    (torch.bfloat16, "bhtd", 16, 5, 4, 128, 7000, 0),   # paged
+    (torch.float32, "bthd", 0, 3, 4, 64, 5000, 0),      # the reference's row layout and type
+    (torch.bfloat16, "bhtd", 0, 40, 2, 128, 300, 0),    # short sequences: chunks hold many whole pairs
+])
+def test_decode_with_small_chunks_handed_out_on_demand(pkg, ctx, dtype, layout, block_size, B, H, D, T, merge_kernel):
+    """The launch of a long batch deals three quarters of the caches out in advance and the rest as small chunks
+    that a CTA takes from a counter when it has finished what it had (knob ``decode_dynamic_chunks``: 1 forces
+    that for any size, 2 forbids it).  Which CTA takes which chunk differs from run to run, the cuts do not: two
+    runs agree bit for bit, both forms agree with the oracle, and with each other within the tolerance (they cut
+    the sums in different places)."""
+    rng = np.random.default_rng(B * 31 + T)
+    lens = [int(x) for x in rng.integers(1, T + 1, size=B)]
+    lens[0] = T
+    if B > 2:
+        lens[1] = 0
+    outs = {}
+    for mode in (1, 1, 2):
+        pkg._native.tune("decode_dynamic_chunks", mode)
+        pkg._native.tune("decode_merge_kernel", merge_kernel)
+        try:
+            got, want = _decode_case(pkg, ctx, dtype, layout, block_size, B=B, H=H, D=D, T_max=T, lens=lens, seed=5)
+        finally:
+            pkg._native.tune("decode_dynamic_chunks", 0)
+            pkg._native.tune("decode_merge_kernel", 0)
+        np.testing.assert_allclose(got, want, **U.TOL[dtype])
+        outs.setdefault(mode, []).append(got)
+    assert np.array_equal(outs[1][0], outs[1][1])
+    np.testing.assert_allclose(outs[1][0], outs[2][0], **U.TOL[dtype])
+
+
+def test_decode_with_chunks_on_demand_replayed_from_a_cuda_graph(pkg, ctx):
+    """The chunk counter of a launch goes back to zero with the launch's last request, so a launch replayed from a
+    CUDA graph (which carries the launch number it was captured with) hands its chunks out afresh every time."""
+    gpu = pkg.gpu
+    B, H, D, T, dtype = 3, 4, 128, 12000, torch.bfloat16
+    E = H * D
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=dtype, layout="bhtd", ragged=True))
+    cache.layers[0].k_cache.buffer.copy_(U.randn((B * H * T, D), dtype, ctx.device, 1))
+    cache.layers[0].v_cache.buffer.copy_(U.randn((B * H * T, D), dtype, ctx.device, 2))
+    gpu.kv_cache_set_lengths(cache, [T, T // 2, 100])
+    cache.current_len = T  # the upper bound that sizes the launch stays fixed
+    q, out = U.randn((B, E), dtype, ctx.device, 3), torch.empty((B, E), dtype=dtype, device=ctx.device)
+    qb, ob = U.buf2d(pkg, ctx, q), U.buf2d(pkg, ctx, out)
+
+    def launch():
+        gpu.batch_begin(ctx)
+        gpu.attention_with_kv_cache(ctx, cache, 0, qb, ob)
+        gpu.batch_commit(ctx)
+
+    pkg._native.tune("decode_dynamic_chunks", 1)
+    try:
+        side = torch.cuda.Stream(device=ctx.device)
+        side.wait_stream(torch.cuda.current_stream(ctx.device))
+        with torch.cuda.stream(side):
+            launch()  # first-use set-up outside the capture
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                launch()
+        torch.cuda.current_stream(ctx.device).wait_stream(side)
+        for i, lens in enumerate([[T, T // 2, 100], [5, T, T], [T - 1, 1, 0], [12345 % T, 6789, 4000]]):
+            q.copy_(U.randn((B, E), dtype, ctx.device, 10 + i))
+            cache.seq_lens.copy_(torch.tensor(lens, dtype=torch.int32))
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            replayed = out.clone()
+            launch()
+            torch.cuda.synchronize()
+            assert torch.equal(replayed.view(torch.int16), out.view(torch.int16)), f"replay {i}"
+            k4 = cache.layers[0].k_cache.buffer.view(B, H, T, D).permute(0, 2, 1, 3)
+            v4 = cache.layers[0].v_cache.buffer.view(B, H, T, D).permute(0, 2, 1, 3)
+            want = U.oracle_decode(q, k4.contiguous(), v4.contiguous(), lens)
+            np.testing.assert_allclose(U.to_f32(replayed), want, **U.TOL[dtype])
+    finally:
+        pkg._native.tune("decode_dynamic_chunks", 0)
+    assert int(ctx.dev_status.item()) == 0

@@ -57,7 +57,7 @@ def test_static_scratch_decode_matches_workspace_decode_twice(pkg, dtype):
 
 
 def test_static_scratch_decode_takes_the_benchmark_shape_and_allocates_nothing(pkg):
-    """B = 64, H = 32, D = 128 bf16 (17 MB of partials at three CTAs per SM) fits the built-in array and is
+    """B = 64, H = 32, D = 128 bf16 (6 MB of partial slots) fits the built-in array and is
     bit-identical to b2kv_decode; the free device memory does not move across a call once the first call on
     the device has looked the array's address up."""
     native = pkg._native
@@ -90,7 +90,8 @@ def test_static_scratch_decode_refuses_shapes_beyond_its_array(pkg):
     native = pkg._native
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    B, H, D, T_upper = 512, 32, 128, 8192  # partials: far more than the built-in array
+    B, H, D, T_upper = 4096, 32, 128, 8192  # one partial slot per (sequence, head) alone: 68 MB, twice the array
+    assert B * H * (D + 2) * 4 > native.STATIC_SCRATCH_BYTES
     tiny = torch.zeros(64, dtype=torch.bfloat16, device=device)  # never dereferenced: the call must fail first
     rc = native.lib.b2kv_decode_static(tiny.data_ptr(), tiny.data_ptr(), tiny.data_ptr(), tiny.data_ptr(), None,
                                        T_upper, 0, B, H, D, T_upper, H * T_upper * D, D, T_upper * D,
