@@ -147,12 +147,14 @@ struct DecodeCfg {
 // piece that has to be merged, so a launch whose equal shares are short (less than 256 tiles: there small chunks
 // were measured to cost more than they even out, 227 against 170 us at 79 tiles per CTA) is dealt out whole, as
 // equal shares.  Interleaved runs at 319 tiles per CTA: 675 us against 695 us for equal shares (long run,
-// power-capped clocks).
+// power-capped clocks).  Nor do small chunks pay where sequences are long against them: four sequences of
+// 131072 tokens and 32 heads ran 1.40 against 1.20 ms, a pair's hundred pieces being merged by one warp at the end.
 
 constexpr int kStaticNum = 3, kStaticDen = 4;  // part of the token space dealt out in advance
 constexpr int kChunksPerShare = 32;            // small chunks that an equal share would be cut into
 constexpr int kMinChunkTiles = 8;              // a small chunk lasts long enough for the merging warp to keep up
 constexpr int kMinDynamicTiles = 256;          // equal shares shorter than this many tiles are dealt out whole
+constexpr int kMaxPiecesPerPair = 16;          // ... and so is a batch whose longest sequence spans more small chunks
 
 // Most chunks of any batch for a grid of `n_ctas` (the small part is at most a quarter of the space plus what
 // rounding adds, a small chunk at least a thirty-second of an equal share).
@@ -161,18 +163,30 @@ __host__ __device__ constexpr int max_chunks(int n_ctas) { return n_ctas * (2 + 
 // Every thread of the calling warp takes part (the lengths are summed across the lanes).
 __device__ __forceinline__ Geometry geometry_of(const DecodeParams& p, int n_ctas, int tile, int lane) {
     long long sum = 0;
-    for (int b = lane; b < p.B; b += 32) sum += seq_len_of(p, b);
+    int longest = 0;
+    for (int b = lane; b < p.B; b += 32) {
+        const int n = seq_len_of(p, b);
+        sum += n;
+        longest = max(longest, n);
+    }
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    for (int off = 16; off >= 1; off >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, off));
+    }
     Geometry ge;
     ge.total = sum * p.H;
     const long long per = (ge.total + n_ctas - 1) / n_ctas;  // an equal share
-    // a short launch is dealt out whole: the small chunks' extra pieces and requests cost more than they even out
-    const bool on_demand = p.dynamic_chunks == 1 || (p.dynamic_chunks == 0 && per >= static_cast<long long>(kMinDynamicTiles) * tile);
-    ge.sa = ((on_demand ? (per * kStaticNum + kStaticDen - 1) / kStaticDen : per) + tile - 1) / tile * tile;
-    if (ge.sa < tile) ge.sa = tile;
     ge.sb = ((per + kChunksPerShare - 1) / kChunksPerShare + tile - 1) / tile * tile;
     if (ge.sb < static_cast<long long>(kMinChunkTiles) * tile) ge.sb = static_cast<long long>(kMinChunkTiles) * tile;
+    // Small chunks only where they pay: not in a short launch (their extra pieces and requests cost more than they
+    // even out), and not where a (sequence, head) would be cut into many of them (its pieces are merged by one
+    // warp, one after the other, at the very end).
+    const bool on_demand = p.dynamic_chunks == 1 ||
+                           (p.dynamic_chunks == 0 && per >= static_cast<long long>(kMinDynamicTiles) * tile &&
+                            ge.sb * kMaxPiecesPerPair >= longest);
+    ge.sa = ((on_demand ? (per * kStaticNum + kStaticDen - 1) / kStaticDen : per) + tile - 1) / tile * tile;
+    if (ge.sa < tile) ge.sa = tile;
     ge.n_static = n_ctas;
     ge.a_end = min(static_cast<long long>(n_ctas) * ge.sa, ge.total);
     ge.n_chunks = n_ctas + static_cast<int>((ge.total - ge.a_end + ge.sb - 1) / ge.sb);
@@ -732,27 +746,46 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) m_g = fmaxf(m_g, __shfl_xor_sync(0xffffffffu, m_g, off));
-        // the weighted sums, piece after piece (a fixed order); a lane's columns of a piece are loaded together
+        // The weighted sums, piece after piece (a fixed order).  A long pair may come in a hundred pieces, so the
+        // loads of four chunks are in flight together (a chunk without a piece of this pair counts with weight 0).
         float l_g = 0.f, og[CPM];
 #pragma unroll
         for (int i = 0; i < CPM; ++i) og[i] = 0.f;
-        for (long long g = g_first; g <= g_last; ++g) {
-            long long s0, s1;
-            chunk_range(ge, g, s0, s1);
-            int t0, t1;
-            piece_of(s0, s1, mt.pair_off, mt.len, TILE_T, t0, t1);
-            if (t0 >= t1) continue;
-            const size_t sl = static_cast<size_t>(piece_slot(g, s0, mt.pair_off));
-            float part[CPM];
+        constexpr int kAhead = 4;
+        for (long long g0 = g_first; g0 <= g_last; g0 += kAhead) {
+            float part[kAhead][CPM], pm[kAhead], pl[kAhead];
+            bool live[kAhead];
 #pragma unroll
-            for (int i = 0; i < CPM; ++i) {
-                const int d = lane + 32 * i;
-                part[i] = d < D ? __ldcg(&p.ws_acc[sl * D + d]) : 0.f;
+            for (int u = 0; u < kAhead; ++u) {
+                const long long g = g0 + u;
+                live[u] = false;
+                pm[u] = 0.f, pl[u] = 0.f;
+#pragma unroll
+                for (int i = 0; i < CPM; ++i) part[u][i] = 0.f;
+                if (g > g_last) continue;
+                long long s0, s1;
+                chunk_range(ge, g, s0, s1);
+                int t0, t1;
+                piece_of(s0, s1, mt.pair_off, mt.len, TILE_T, t0, t1);
+                if (t0 >= t1) continue;
+                live[u] = true;
+                const size_t sl = static_cast<size_t>(piece_slot(g, s0, mt.pair_off));
+                pm[u] = __ldcg(&p.ws_ml[sl * 2]);
+                pl[u] = __ldcg(&p.ws_ml[sl * 2 + 1]);
+#pragma unroll
+                for (int i = 0; i < CPM; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < D) part[u][i] = __ldcg(&p.ws_acc[sl * D + d]);
+                }
             }
-            const float wg = exp2f(__ldcg(&p.ws_ml[sl * 2]) - m_g);
-            l_g += wg * __ldcg(&p.ws_ml[sl * 2 + 1]);
 #pragma unroll
-            for (int i = 0; i < CPM; ++i) og[i] += wg * part[i];
+            for (int u = 0; u < kAhead; ++u) {
+                if (!live[u]) continue;
+                const float wg = exp2f(pm[u] - m_g);
+                l_g += wg * pl[u];
+#pragma unroll
+                for (int i = 0; i < CPM; ++i) og[i] += wg * part[u][i];
+            }
         }
         T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(bh) * D;
 #pragma unroll
