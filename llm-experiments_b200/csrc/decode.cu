@@ -297,141 +297,141 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
     // this CTA's chunks: its own advance chunk, then small ones as long as the counter has some
     for (long long chunk = blockIdx.x; ok && chunk < ge.n_chunks;) {
-    long long c_start, c_end;
-    chunk_range(ge, chunk, c_start, c_end);
-    // Ask for the chunk after this one now.  Every CTA asks until it is turned away, so the launch's last request
-    // is known by its number and puts the counter back to zero (for a launch replayed from a CUDA graph).
-    long long chunk_next = ge.n_chunks;
-    if (on_demand) {
-        if (lane == 0) chunk_next = claim_chunk(p, ge);
-        chunk_next = __shfl_sync(0xffffffffu, chunk_next, 0);
-    }
-    // first (sequence, head) that the chunk touches
-    int b = p.B;
-    long long tok_before = 0;  // tokens of the sequences that precede b
-    int len_b = 0;
-    if (c_start < c_end) locate_sequence(p, c_start, lane, b, tok_before, len_b);
-    int h = (b < p.B) ? static_cast<int>((c_start - tok_before * p.H) / len_b) : 0;
-
-    while (ok && b < p.B) {
-        const long long pair_off = tok_before * p.H + static_cast<long long>(h) * len_b;
-        if (pair_off >= c_end) break;
-        int t_begin, t_end;
-        piece_of(c_start, c_end, pair_off, len_b, TILE_T, t_begin, t_end);
-        // how many chunks hold a piece with tokens of this pair (the merge counts them in)
-        int pieces = 0;
-        {
-            const long long g_first = chunk_of(ge, pair_off), g_last = chunk_of(ge, pair_off + len_b - 1);
-            for (long long g = g_first + lane; g <= g_last; g += 32) {
-                long long s0, s1;
-                chunk_range(ge, g, s0, s1);
-                int t0, t1;
-                piece_of(s0, s1, pair_off, len_b, TILE_T, t0, t1);
-                pieces += (t0 < t1) ? 1 : 0;
-            }
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) pieces += __shfl_xor_sync(0xffffffffu, pieces, off);
+        long long c_start, c_end;
+        chunk_range(ge, chunk, c_start, c_end);
+        // Ask for the chunk after this one now.  Every CTA asks until it is turned away, so the launch's last request
+        // is known by its number and puts the counter back to zero (for a launch replayed from a CUDA graph).
+        long long chunk_next = ge.n_chunks;
+        if (on_demand) {
+            if (lane == 0) chunk_next = claim_chunk(p, ge);
+            chunk_next = __shfl_sync(0xffffffffu, chunk_next, 0);
         }
-        // a pair in one piece has a slot of its own (used when a merge kernel follows), a piece of several is one
-        // of its chunk's two
-        const int bh = b * p.H + h;
-        int slot = pieces == 1 ? p.n_slots - p.B * p.H + bh : piece_slot(chunk, c_start, pair_off);
-        if (t_begin < t_end && (slot < 0 || slot >= p.n_slots)) {
-            report_status(p.dev_status, B2KV_DEV_BAD_POSITION);  // cannot happen: sized on the host
-            t_end = t_begin;
-            slot = 0;
-        }
+        // first (sequence, head) that the chunk touches
+        int b = p.B;
+        long long tok_before = 0;  // tokens of the sequences that precede b
+        int len_b = 0;
+        if (c_start < c_end) locate_sequence(p, c_start, lane, b, tok_before, len_b);
+        int h = (b < p.B) ? static_cast<int>((c_start - tok_before * p.H) / len_b) : 0;
 
-        for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
-            const int ntok = min(TILE_T, t_end - t0);
-            // paged: this lane's block of the tile is looked up before the wait for a free stage, so that the table's
-            // latency falls into that wait and not between a stage coming free and its copies going out
-            int blk_ahead = -1;
-            if (p.block_table != nullptr && !p.use_tensor_map) {
-                const int tok = t0 + lane * p.run_len;
-                if (tok < t0 + ntok) blk_ahead = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+        while (ok && b < p.B) {
+            const long long pair_off = tok_before * p.H + static_cast<long long>(h) * len_b;
+            if (pair_off >= c_end) break;
+            int t_begin, t_end;
+            piece_of(c_start, c_end, pair_off, len_b, TILE_T, t_begin, t_end);
+            // how many chunks hold a piece with tokens of this pair (the merge counts them in)
+            int pieces = 0;
+            {
+                const long long g_first = chunk_of(ge, pair_off), g_last = chunk_of(ge, pair_off + len_b - 1);
+                for (long long g = g_first + lane; g <= g_last; g += 32) {
+                    long long s0, s1;
+                    chunk_range(ge, g, s0, s1);
+                    int t0, t1;
+                    piece_of(s0, s1, pair_off, len_b, TILE_T, t0, t1);
+                    pieces += (t0 < t1) ? 1 : 0;
+                }
+    #pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) pieces += __shfl_xor_sync(0xffffffffu, pieces, off);
             }
-            if (!mbar_wait(&empty[stage], phase ^ 1u)) {
-                ok = false;
-                break;
+            // a pair in one piece has a slot of its own (used when a merge kernel follows), a piece of several is one
+            // of its chunk's two
+            const int bh = b * p.H + h;
+            int slot = pieces == 1 ? p.n_slots - p.B * p.H + bh : piece_slot(chunk, c_start, pair_off);
+            if (t_begin < t_end && (slot < 0 || slot >= p.n_slots)) {
+                report_status(p.dev_status, B2KV_DEV_BAD_POSITION);  // cannot happen: sized on the host
+                t_end = t_begin;
+                slot = 0;
             }
-            uint8_t* sbase = stages + static_cast<size_t>(stage) * Cfg::kStageBytes;
-            const bool first = (t0 == t_begin);
-            if (lane == 0) {
-                StageMeta mt;
-                mt.slot = slot;
-                mt.ntok = ntok;
-                mt.flags = (first ? kFlagFirst : 0) | (t0 + TILE_T >= t_end ? kFlagLast : 0) | (pieces == 1 ? kFlagWhole : 0);
-                mt.pieces = pieces;
-                mt.pair_off = pair_off;
-                mt.len = len_b;
-                mt.bh = bh;
-                meta[stage] = mt;
-                // a tiled load always delivers the whole box (rows past the end arrive as zeros or as
-                // the next rows of the cache; the consumers use the first ntok only)
-                const uint32_t rows = p.use_tensor_map ? static_cast<uint32_t>(TILE_T) : static_cast<uint32_t>(ntok);
-                const uint32_t bytes = 2u * rows * Cfg::kRowBytes + (first ? Cfg::kRowBytes : 0);
-                mbar_arrive_expect_tx(&full[stage], bytes);
-            }
-            __syncwarp();
-            if (first && lane == 31) {
-                bulk_g2s(sbase + 2 * Cfg::kTileBytes,
-                         qbase + (static_cast<size_t>(b) * p.H + h) * Cfg::kRowBytes, Cfg::kRowBytes, &full[stage]);
-            }
-            if (p.use_tensor_map) {
-                if (lane == 0) tma_load_4d(sbase, tm_k, &full[stage], 0, t0, h, b);
-                if (lane == 1) tma_load_4d(sbase + Cfg::kTileBytes, tm_v, &full[stage], 0, t0, h, b);
+
+            for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
+                const int ntok = min(TILE_T, t_end - t0);
+                // paged: this lane's block of the tile is looked up before the wait for a free stage, so that the table's
+                // latency falls into that wait and not between a stage coming free and its copies going out
+                int blk_ahead = -1;
+                if (p.block_table != nullptr && !p.use_tensor_map) {
+                    const int tok = t0 + lane * p.run_len;
+                    if (tok < t0 + ntok) blk_ahead = p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+                }
+                if (!mbar_wait(&empty[stage], phase ^ 1u)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* sbase = stages + static_cast<size_t>(stage) * Cfg::kStageBytes;
+                const bool first = (t0 == t_begin);
+                if (lane == 0) {
+                    StageMeta mt;
+                    mt.slot = slot;
+                    mt.ntok = ntok;
+                    mt.flags = (first ? kFlagFirst : 0) | (t0 + TILE_T >= t_end ? kFlagLast : 0) | (pieces == 1 ? kFlagWhole : 0);
+                    mt.pieces = pieces;
+                    mt.pair_off = pair_off;
+                    mt.len = len_b;
+                    mt.bh = bh;
+                    meta[stage] = mt;
+                    // a tiled load always delivers the whole box (rows past the end arrive as zeros or as
+                    // the next rows of the cache; the consumers use the first ntok only)
+                    const uint32_t rows = p.use_tensor_map ? static_cast<uint32_t>(TILE_T) : static_cast<uint32_t>(ntok);
+                    const uint32_t bytes = 2u * rows * Cfg::kRowBytes + (first ? Cfg::kRowBytes : 0);
+                    mbar_arrive_expect_tx(&full[stage], bytes);
+                }
+                __syncwarp();
+                if (first && lane == 31) {
+                    bulk_g2s(sbase + 2 * Cfg::kTileBytes,
+                             qbase + (static_cast<size_t>(b) * p.H + h) * Cfg::kRowBytes, Cfg::kRowBytes, &full[stage]);
+                }
+                if (p.use_tensor_map) {
+                    if (lane == 0) tma_load_4d(sbase, tm_k, &full[stage], 0, t0, h, b);
+                    if (lane == 1) tma_load_4d(sbase + Cfg::kTileBytes, tm_v, &full[stage], 0, t0, h, b);
+                    ++fills;
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    continue;
+                }
+                const int nruns = (ntok + p.run_len - 1) / p.run_len;
+                for (int r = lane; r < nruns; r += 32) {
+                    const int tok = t0 + r * p.run_len;
+                    const int cnt = min(p.run_len, t0 + ntok - tok);
+                    int64_t off;
+                    if (p.block_table == nullptr) {
+                        off = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(tok) * p.stride_t;
+                    } else {
+                        int blk = r == lane ? blk_ahead : p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
+                        if (blk < 0 || blk >= p.n_blocks) {
+                            report_status(p.dev_status, B2KV_DEV_BAD_BLOCK);
+                            blk = 0;  // stay inside the pool; the status word tells the caller
+                        }
+                        off = static_cast<int64_t>(blk) * p.stride_b +
+                              static_cast<int64_t>(tok % p.block_size) * p.stride_t;
+                    }
+                    off = (off + static_cast<int64_t>(h) * p.stride_h) * static_cast<int64_t>(sizeof(T));
+                    const uint32_t bytes = static_cast<uint32_t>(cnt) * Cfg::kRowBytes;
+                    const int dst = (tok - t0) * Cfg::kRowBytes;
+                    if (p.l2_evict_first) {
+                        bulk_g2s_hint(sbase + dst, kbase + off, bytes, &full[stage], l2_policy);
+                        bulk_g2s_hint(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage], l2_policy);
+                    } else {
+                        bulk_g2s(sbase + dst, kbase + off, bytes, &full[stage]);
+                        bulk_g2s(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage]);
+                    }
+                }
                 ++fills;
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
-                continue;
             }
-            const int nruns = (ntok + p.run_len - 1) / p.run_len;
-            for (int r = lane; r < nruns; r += 32) {
-                const int tok = t0 + r * p.run_len;
-                const int cnt = min(p.run_len, t0 + ntok - tok);
-                int64_t off;
-                if (p.block_table == nullptr) {
-                    off = static_cast<int64_t>(b) * p.stride_b + static_cast<int64_t>(tok) * p.stride_t;
-                } else {
-                    int blk = r == lane ? blk_ahead : p.block_table[static_cast<int64_t>(b) * p.max_blocks + tok / p.block_size];
-                    if (blk < 0 || blk >= p.n_blocks) {
-                        report_status(p.dev_status, B2KV_DEV_BAD_BLOCK);
-                        blk = 0;  // stay inside the pool; the status word tells the caller
-                    }
-                    off = static_cast<int64_t>(blk) * p.stride_b +
-                          static_cast<int64_t>(tok % p.block_size) * p.stride_t;
-                }
-                off = (off + static_cast<int64_t>(h) * p.stride_h) * static_cast<int64_t>(sizeof(T));
-                const uint32_t bytes = static_cast<uint32_t>(cnt) * Cfg::kRowBytes;
-                const int dst = (tok - t0) * Cfg::kRowBytes;
-                if (p.l2_evict_first) {
-                    bulk_g2s_hint(sbase + dst, kbase + off, bytes, &full[stage], l2_policy);
-                    bulk_g2s_hint(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage], l2_policy);
-                } else {
-                    bulk_g2s(sbase + dst, kbase + off, bytes, &full[stage]);
-                    bulk_g2s(sbase + Cfg::kTileBytes + dst, vbase + off, bytes, &full[stage]);
-                }
-            }
-            ++fills;
-            if (++stage == STAGES) {
-                stage = 0;
-                phase ^= 1u;
+            // next (sequence, head); empty sequences own no tokens and are skipped
+            if (++h == p.H) {
+                h = 0;
+                tok_before += len_b;
+                do {
+                    ++b;
+                    len_b = (b < p.B) ? seq_len_of(p, b) : 0;
+                } while (b < p.B && len_b == 0);
             }
         }
-        // next (sequence, head); empty sequences own no tokens and are skipped
-        if (++h == p.H) {
-            h = 0;
-            tok_before += len_b;
-            do {
-                ++b;
-                len_b = (b < p.B) ? seq_len_of(p, b) : 0;
-            } while (b < p.B && len_b == 0);
-        }
-    }
-    chunk = chunk_next;
+        chunk = chunk_next;
     }
 
     if (ok && mbar_wait(&empty[stage], phase ^ 1u)) {
