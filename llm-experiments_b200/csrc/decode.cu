@@ -85,7 +85,7 @@ struct DecodeParams {
     // Merge inside the split kernel (plain decode only): the CTA that finishes the last piece of a (sequence, head)
     // merges the pair's partials and writes the output row, so that no second launch is needed.
     void* fused_out;                 // output [B, H*D] of the storage type; null = the merge kernel writes it
-    unsigned long long* ws_tickets;  // [B*H]: (call number << 16) | pieces of the pair finished in that call
+    unsigned long long* ws_tickets;  // [B*H]: (low 40 bits of the call number << 24) | pieces of the pair finished in that call
     unsigned long long call_id;      // unique per launch call, 48 bits, never 0: tickets left by other calls never count
                                      // (a finished pair's ticket goes back to 0, for launches replayed from a graph)
     int dynamic_chunks;              // 0: by the size of the batch, 1: always, 2: never hand out small chunks on demand
@@ -254,20 +254,25 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
     }
 }
 
-// Takes the next small chunk from the launch's counter (a number past the last chunk: none is left).  The counter
-// word carries the launch's number above its count, so that whatever another launch or an uninitialised workspace
-// left there never counts: the first CTAs to arrive put the launch's number in (one compare-and-swap each; a CTA
-// that loses sees the number and goes on), everybody then counts with a plain atomic add, which needs no retries
-// however many CTAs ask at once.
-__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge) {
-    const unsigned long long tag = (p.call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
-    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(p.ws_counter);
+// Counters in the workspace (the chunk counter, the tickets of the pairs) carry the launch's number above their
+// count, so that whatever another launch or an uninitialised workspace left there never counts: the first CTAs to
+// arrive put the launch's number in (one compare-and-swap each; a CTA that loses sees the number and goes on),
+// everybody then counts with a plain atomic add, which needs no retries however many CTAs come at once.  Returns
+// the count with this arrival included.  claim_chunk takes the next small chunk from the launch's counter (a number
+// past the last chunk: none is left).
+__device__ __forceinline__ long long tagged_count(unsigned long long* word, unsigned long long call_id) {
+    const unsigned long long tag = (call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
+    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(word);
     while ((seen & ~0xffffffull) != tag) {
-        const unsigned long long old = atomicCAS(p.ws_counter, seen, tag);
+        const unsigned long long old = atomicCAS(word, seen, tag);
         if (old == seen) break;
         seen = old;
     }
-    const long long asked = static_cast<long long>(atomicAdd(p.ws_counter, 1ull) & 0xffffffull) + 1;  // this request included
+    return static_cast<long long>(atomicAdd(word, 1ull) & 0xffffffull) + 1;  // this request included
+}
+
+__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge) {
+    const long long asked = tagged_count(p.ws_counter, p.call_id);
     // Every CTA asks until it is turned away: small chunks + CTAs requests in all.  The last one leaves a zero (a
     // launch replayed from a CUDA graph carries the number it was captured with and must not count on).
     if (asked == static_cast<long long>(ge.n_chunks - ge.n_static) + ge.n_static) *p.ws_counter = 0ull;
@@ -719,17 +724,7 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         __syncwarp();
         const int bh = mt.bh;
         int last = 0;
-        if (lane == 0) {
-            unsigned long long* t = p.ws_tickets + bh;
-            unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(t), next;
-            while (true) {
-                const unsigned long long assumed = seen;
-                next = (assumed >> 16) == p.call_id ? assumed + 1ull : ((p.call_id << 16) | 1ull);
-                seen = atomicCAS(t, assumed, next);
-                if (seen == assumed) break;
-            }
-            last = (static_cast<int>(next & 0xffffull) == mt.pieces) ? 1 : 0;
-        }
+        if (lane == 0) last = tagged_count(p.ws_tickets + bh, p.call_id) == static_cast<long long>(mt.pieces) ? 1 : 0;
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last == 0) continue;
         __threadfence();
