@@ -213,10 +213,10 @@ int b2kv_merge_partials(const float* parts, int R, int B, int H, int D, void* ou
  *     2 * (10 * CTAs + 2) + B * H slots of (D + 2) * 4 bytes (two per chunk of work that the
  *     launch may cut the caches into, one per (sequence, head)), plus 8 bytes per (sequence,
  *     head) for the tickets and 8 for the chunk counter, where CTAs is the persistent grid:
- *     the SM count times the resident CTAs per SM of the compiled variant (three for 256-byte
+ *     the SM count times the resident CTAs per SM of the compiled variant (two for 256-byte
  *     rows, at most four for any row size), and never more than the tiles of work.  The
- *     benchmark shape (B=64, H=32, D=128, bf16; 444 CTAs on a 148-SM B200) needs 10932 slots
- *     = 5.7 MB and fits; B=4096 with the same heads does not.
+ *     benchmark shape (B=64, H=32, D=128, bf16; 296 CTAs on a 148-SM B200) needs 7972 slots
+ *     = 4.1 MB and fits; B=4096 with the same heads does not.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current).  Make that first call before starting
  *     any stream capture on that device.

@@ -57,7 +57,7 @@ def test_static_scratch_decode_matches_workspace_decode_twice(pkg, dtype):
 
 
 def test_static_scratch_decode_takes_the_benchmark_shape_and_allocates_nothing(pkg):
-    """B = 64, H = 32, D = 128 bf16 (6 MB of partial slots) fits the built-in array and is
+    """B = 64, H = 32, D = 128 bf16 (4 MB of partial slots) fits the built-in array and is
     bit-identical to b2kv_decode; the free device memory does not move across a call once the first call on
     the device has looked the array's address up."""
     native = pkg._native
