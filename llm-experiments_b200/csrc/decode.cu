@@ -260,19 +260,22 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
 // everybody then counts with a plain atomic add, which needs no retries however many CTAs come at once.  Returns
 // the count with this arrival included.  claim_chunk takes the next small chunk from the launch's counter (a number
 // past the last chunk: none is left).
-__device__ __forceinline__ long long tagged_count(unsigned long long* word, unsigned long long call_id) {
-    const unsigned long long tag = (call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
-    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(word);
-    while ((seen & ~0xffffffull) != tag) {
-        const unsigned long long old = atomicCAS(word, seen, tag);
-        if (old == seen) break;
-        seen = old;
+__device__ __forceinline__ long long tagged_count(unsigned long long* word, unsigned long long call_id,
+                                                  bool installed = false) {
+    if (!installed) {  // (a caller that has counted on this word before in this launch knows the number is in)
+        const unsigned long long tag = (call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(word);
+        while ((seen & ~0xffffffull) != tag) {
+            const unsigned long long old = atomicCAS(word, seen, tag);
+            if (old == seen) break;
+            seen = old;
+        }
     }
     return static_cast<long long>(atomicAdd(word, 1ull) & 0xffffffull) + 1;  // this request included
 }
 
-__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge) {
-    const long long asked = tagged_count(p.ws_counter, p.call_id);
+__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge, bool installed) {
+    const long long asked = tagged_count(p.ws_counter, p.call_id, installed);
     // Every CTA asks until it is turned away: small chunks + CTAs requests in all.  The last one leaves a zero (a
     // launch replayed from a CUDA graph carries the number it was captured with and must not count on).
     if (asked == static_cast<long long>(ge.n_chunks - ge.n_static) + ge.n_static) *p.ws_counter = 0ull;
@@ -299,24 +302,47 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
     const Geometry ge = geometry_of(p, gridDim.x, TILE_T, lane);
     if (lane == 0) *geo = ge;  // (published to the other warps with the first stage's barrier)
     const bool on_demand = ge.n_chunks > ge.n_static;
+    bool asked_before = false;  // this CTA has counted on the chunk counter in this launch
+
+    // Where a chunk begins: its range and the first (sequence, head) that it touches.
+    struct ChunkStart {
+        long long c_start, c_end;
+        long long tok_before;  // tokens of the sequences that precede b
+        int b, len_b, h;
+    };
+    auto chunk_start = [&](long long g) {
+        ChunkStart cs;
+        chunk_range(ge, g, cs.c_start, cs.c_end);
+        cs.b = p.B;
+        cs.tok_before = 0;
+        cs.len_b = 0;
+        if (cs.c_start < cs.c_end) locate_sequence(p, cs.c_start, lane, cs.b, cs.tok_before, cs.len_b);
+        cs.h = (cs.b < p.B) ? static_cast<int>((cs.c_start - cs.tok_before * p.H) / cs.len_b) : 0;
+        return cs;
+    };
 
     // this CTA's chunks: its own advance chunk, then small ones as long as the counter has some
+    ChunkStart coming = chunk_start(blockIdx.x);
     for (long long chunk = blockIdx.x; ok && chunk < ge.n_chunks;) {
-        long long c_start, c_end;
-        chunk_range(ge, chunk, c_start, c_end);
-        // Ask for the chunk after this one now.  Every CTA asks until it is turned away, so the launch's last request
-        // is known by its number and puts the counter back to zero (for a launch replayed from a CUDA graph).
+        const long long c_start = coming.c_start, c_end = coming.c_end;
+        long long tok_before = coming.tok_before;
+        int b = coming.b, len_b = coming.len_b, h = coming.h;
+        // The chunk after this one is asked for, and its beginning looked up, once this one's first tile is on its
+        // way: the request is one or two round trips to L2 and the look-up a few hundred instructions, which at
+        // the head of a chunk would hold its copies back (2.5 us per chunk, measured).  Every CTA asks until it is
+        // turned away, so the launch's last request is known by its number and puts the counter back to zero (for
+        // a launch replayed from a CUDA graph).
         long long chunk_next = ge.n_chunks;
-        if (on_demand) {
-            if (lane == 0) chunk_next = claim_chunk(p, ge);
+        bool asked = !on_demand;
+        int tiles_issued = 0;
+        auto ask = [&]() {
+            if (asked) return;
+            if (lane == 0) chunk_next = claim_chunk(p, ge, asked_before);
             chunk_next = __shfl_sync(0xffffffffu, chunk_next, 0);
-        }
-        // first (sequence, head) that the chunk touches
-        int b = p.B;
-        long long tok_before = 0;  // tokens of the sequences that precede b
-        int len_b = 0;
-        if (c_start < c_end) locate_sequence(p, c_start, lane, b, tok_before, len_b);
-        int h = (b < p.B) ? static_cast<int>((c_start - tok_before * p.H) / len_b) : 0;
+            asked = true;
+            asked_before = true;
+            if (chunk_next < ge.n_chunks) coming = chunk_start(chunk_next);
+        };
 
         while (ok && b < p.B) {
             const long long pair_off = tok_before * p.H + static_cast<long long>(h) * len_b;
@@ -349,6 +375,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
 
             for (int t0 = t_begin; t0 < t_end; t0 += TILE_T) {
                 const int ntok = min(TILE_T, t_end - t0);
+                if (tiles_issued++ == 1) ask();
                 // paged: this lane's block of the tile is looked up before the wait for a free stage, so that the table's
                 // latency falls into that wait and not between a stage coming free and its copies going out
                 int blk_ahead = -1;
@@ -436,6 +463,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
                 } while (b < p.B && len_b == 0);
             }
         }
+        ask();
         chunk = chunk_next;
     }
 
