@@ -257,25 +257,26 @@ __device__ __forceinline__ void locate_sequence(const DecodeParams& p, long long
 // Counters in the workspace (the chunk counter, the tickets of the pairs) carry the launch's number above their
 // count, so that whatever another launch or an uninitialised workspace left there never counts: the first CTAs to
 // arrive put the launch's number in (one compare-and-swap each; a CTA that loses sees the number and goes on),
-// everybody then counts with a plain atomic add, which needs no retries however many CTAs come at once.  Returns
-// the count with this arrival included.  claim_chunk takes the next small chunk from the launch's counter (a number
+// everybody counts with a plain atomic add, which needs no retries however many CTAs come at once and is a
+// single round trip to L2 once the number is in.  Returns the count with this arrival included.  claim_chunk takes the next small chunk from the launch's counter (a number
 // past the last chunk: none is left).
-__device__ __forceinline__ long long tagged_count(unsigned long long* word, unsigned long long call_id,
-                                                  bool installed = false) {
-    if (!installed) {  // (a caller that has counted on this word before in this launch knows the number is in)
-        const unsigned long long tag = (call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
-        unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(word);
-        while ((seen & ~0xffffffull) != tag) {
-            const unsigned long long old = atomicCAS(word, seen, tag);
-            if (old == seen) break;
-            seen = old;
-        }
+__device__ __forceinline__ long long tagged_count(unsigned long long* word, unsigned long long call_id) {
+    const unsigned long long tag = (call_id % ((1ull << 40) - 1ull) + 1ull) << 24;
+    // Count first: where the launch's number is in already (every arrival but a word's first few), that is all.
+    unsigned long long old = atomicAdd(word, 1ull);
+    if ((old & ~0xffffffull) == tag) return static_cast<long long>(old & 0xffffffull) + 1;
+    // It was not (this arrival counted on whatever the word held): put it in, or find it put in, and count again.
+    unsigned long long seen = old + 1ull;
+    while ((seen & ~0xffffffull) != tag) {
+        old = atomicCAS(word, seen, tag);
+        if (old == seen) break;
+        seen = old;
     }
     return static_cast<long long>(atomicAdd(word, 1ull) & 0xffffffull) + 1;  // this request included
 }
 
-__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge, bool installed) {
-    const long long asked = tagged_count(p.ws_counter, p.call_id, installed);
+__device__ __forceinline__ long long claim_chunk(const DecodeParams& p, const Geometry& ge) {
+    const long long asked = tagged_count(p.ws_counter, p.call_id);
     // Every CTA asks until it is turned away: small chunks + CTAs requests in all.  The last one leaves a zero (a
     // launch replayed from a CUDA graph carries the number it was captured with and must not count on).
     if (asked == static_cast<long long>(ge.n_chunks - ge.n_static) + ge.n_static) *p.ws_counter = 0ull;
@@ -302,7 +303,6 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
     const Geometry ge = geometry_of(p, gridDim.x, TILE_T, lane);
     if (lane == 0) *geo = ge;  // (published to the other warps with the first stage's barrier)
     const bool on_demand = ge.n_chunks > ge.n_static;
-    bool asked_before = false;  // this CTA has counted on the chunk counter in this launch
 
     // Where a chunk begins: its range and the first (sequence, head) that it touches.
     struct ChunkStart {
@@ -328,7 +328,7 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
         long long tok_before = coming.tok_before;
         int b = coming.b, len_b = coming.len_b, h = coming.h;
         // The chunk after this one is asked for, and its beginning looked up, once this one's first tile is on its
-        // way: the request is one or two round trips to L2 and the look-up a few hundred instructions, which at
+        // way: the request is a round trip to L2 and the look-up a few hundred instructions, which at
         // the head of a chunk would hold its copies back (2.5 us per chunk, measured).  Every CTA asks until it is
         // turned away, so the launch's last request is known by its number and puts the counter back to zero (for
         // a launch replayed from a CUDA graph).
@@ -337,10 +337,9 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
         int tiles_issued = 0;
         auto ask = [&]() {
             if (asked) return;
-            if (lane == 0) chunk_next = claim_chunk(p, ge, asked_before);
+            if (lane == 0) chunk_next = claim_chunk(p, ge);
             chunk_next = __shfl_sync(0xffffffffu, chunk_next, 0);
             asked = true;
-            asked_before = true;
             if (chunk_next < ge.n_chunks) coming = chunk_start(chunk_next);
         };
 
@@ -758,31 +757,18 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         __threadfence();
         const Geometry ge = *geo;
         const long long g_first = chunk_of(ge, mt.pair_off), g_last = chunk_of(ge, mt.pair_off + mt.len - 1);
-        // the pieces' common maximum: the lanes share the chunks out
-        float m_g = -INFINITY;
-        for (long long g = g_first + lane; g <= g_last; g += 32) {
-            long long s0, s1;
-            chunk_range(ge, g, s0, s1);
-            int t0, t1;
-            piece_of(s0, s1, mt.pair_off, mt.len, TILE_T, t0, t1);
-            if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[static_cast<size_t>(piece_slot(g, s0, mt.pair_off)) * 2]));
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) m_g = fmaxf(m_g, __shfl_xor_sync(0xffffffffu, m_g, off));
-        // The weighted sums, piece after piece (a fixed order).  A long pair may come in a hundred pieces, so the
-        // loads of four chunks are in flight together (a chunk without a piece of this pair counts with weight 0).
-        float l_g = 0.f, og[CPM];
-#pragma unroll
-        for (int i = 0; i < CPM; ++i) og[i] = 0.f;
+        // The weighted sums, piece after piece (a fixed order), the loads of four chunks in flight together (a long
+        // pair may come in a hundred pieces; a chunk without a piece of this pair counts with weight 0).  Up to four
+        // chunks - the usual case - are one round trip to L2: their maxima come with the same loads.
         constexpr int kAhead = 4;
-        for (long long g0 = g_first; g0 <= g_last; g0 += kAhead) {
-            float part[kAhead][CPM], pm[kAhead], pl[kAhead];
-            bool live[kAhead];
+        float part[kAhead][CPM], pm[kAhead], pl[kAhead];
+        bool live[kAhead];
+        auto load_pieces = [&](long long g0) {
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
                 const long long g = g0 + u;
                 live[u] = false;
-                pm[u] = 0.f, pl[u] = 0.f;
+                pm[u] = -INFINITY, pl[u] = 0.f;
 #pragma unroll
                 for (int i = 0; i < CPM; ++i) part[u][i] = 0.f;
                 if (g > g_last) continue;
@@ -801,6 +787,11 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
                     if (d < D) part[u][i] = __ldcg(&p.ws_acc[sl * D + d]);
                 }
             }
+        };
+        float m_g = -INFINITY, l_g = 0.f, og[CPM];
+#pragma unroll
+        for (int i = 0; i < CPM; ++i) og[i] = 0.f;
+        auto add_pieces = [&]() {
 #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
                 if (!live[u]) continue;
@@ -808,6 +799,27 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
                 l_g += wg * pl[u];
 #pragma unroll
                 for (int i = 0; i < CPM; ++i) og[i] += wg * part[u][i];
+            }
+        };
+        if (g_last - g_first < kAhead) {
+            load_pieces(g_first);
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) m_g = fmaxf(m_g, pm[u]);
+            add_pieces();
+        } else {
+            // the pieces' common maximum first: the lanes share the chunks out
+            for (long long g = g_first + lane; g <= g_last; g += 32) {
+                long long s0, s1;
+                chunk_range(ge, g, s0, s1);
+                int t0, t1;
+                piece_of(s0, s1, mt.pair_off, mt.len, TILE_T, t0, t1);
+                if (t0 < t1) m_g = fmaxf(m_g, __ldcg(&p.ws_ml[static_cast<size_t>(piece_slot(g, s0, mt.pair_off)) * 2]));
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) m_g = fmaxf(m_g, __shfl_xor_sync(0xffffffffu, m_g, off));
+            for (long long g0 = g_first; g0 <= g_last; g0 += kAhead) {
+                load_pieces(g0);
+                add_pieces();
             }
         }
         T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(bh) * D;
