@@ -408,6 +408,8 @@ def test_decode_replayed_from_a_cuda_graph(pkg, ctx):
     (torch.bfloat16, "bhtd", 16, 5, 4, 128, 7000, 0),   # paged
     (torch.float32, "bthd", 0, 3, 4, 64, 5000, 0),      # the reference's row layout and type
     (torch.bfloat16, "bhtd", 0, 40, 2, 128, 300, 0),    # short sequences: chunks hold many whole pairs
+    (torch.bfloat16, "bhtd", 0, 300, 2, 64, 260, 0),    # more sequences than a warp scans at once, 128-byte rows
+    (torch.float32, "bhtd", 0, 70, 1, 256, 900, 1),     # one head, 1 KB rows, through the merge kernel
 ])
 def test_decode_with_small_chunks_handed_out_on_demand(pkg, ctx, dtype, layout, block_size, B, H, D, T, merge_kernel):
     """The launch of a long batch deals three quarters of the caches out in advance and the rest as small chunks
