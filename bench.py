@@ -379,7 +379,7 @@ def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False, assign="cont
         gpu.batch_begin(ctx)
         gpu.kv_cache_update(ctx, cache, 0, nk_b, nv_b)
         if fused is not None:
-            full = fused.decode(ctx, cache, 0, q_b)  # the merge kernel stores into every rank's buffer
+            full = fused.decode(ctx, cache, 0, q_b)  # the decode kernel stores into every rank's buffer
         else:
             gpu.attention_with_kv_cache(ctx, cache, 0, q_b, out_b)
             full = None
@@ -433,10 +433,10 @@ def run_decode(h: Harness, w, *, gather="nccl", cpu_baseline=False, assign="cont
 
     default_variant = (not h.tuned) and not bs and D == 128
     traffic = int(DRAM_BYTES_PER_TOKEN_HEAD * float(np.sum(lens0 + 1)) * H) if default_variant else None
-    launches_per_step = 2 + (2 if fused is not None else 0)  # append, split (+ merge and flag wait of the fused gather)
+    launches_per_step = 2 + (1 if fused is not None else 0)  # append, split (+ the flag wait of the fused gather)
     if head_split:
         par = (f"heads split x{world}, outputs gathered "
-               + ("by peer stores fused into the merge kernel" if fused is not None
+               + ("by peer stores fused into the decode kernel" if fused is not None
                   else "with one NCCL all-gather per step"))
     elif strong:
         par = (f"the batch cut into {world} sets of {B_total}/{world} sequences ("

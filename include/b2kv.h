@@ -155,18 +155,19 @@ int b2kv_decode_paged(const void* q, const void* k_pool, const void* v_pool, voi
 /*
  * Decode attention of the head-split configuration fused with the all-gather of its outputs.
  * No counterpart in the reference (which is single-device).  Rank r of `world` ranks holds heads
- * [r*H_local, (r+1)*H_local) of every sequence.  The merge kernel stores each output row
- * straight into the [B, H_total*D] output buffers of ALL ranks (peer_out[w], peer-mapped device
- * memory, plain stores over NVLink) at this rank's head offset; its last CTA then writes `epoch`
- * into word `rank` of every rank's flag array (peer_flags[w]).  A final one-warp kernel waits, with
+ * [r*H_local, (r+1)*H_local) of every sequence.  The decode kernel itself stores each output row - from
+ * the warp of the CTA that finishes the row - straight into the [B, H_total*D] output buffers of ALL
+ * ranks (peer_out[w], peer-mapped device memory, plain stores over NVLink) at this rank's head offset;
+ * the last CTA of the launch to finish then writes `epoch` into word `rank` of every rank's flag array
+ * (peer_flags[w]).  A final one-warp kernel waits, with
  * a bound of about two seconds, until all `world` words of this rank's own flags (my_flags) have
  * reached `epoch`; after it, peer_out[rank] holds the outputs of all heads, in stream order.
  * (my_flags == NULL queues no wait kernel: the caller then orders the consumption itself.)
  *   peer_out, peer_flags  device arrays of `world` pointers (the same on every rank up to
  *                         address translation); flags are uint32[world], zeroed once.
- *   counter               local uint32, zeroed once; counts finished merge CTAs for ever.
- *   counter_target        value of the counter after this call = previous target + B*H_local
- *                         (mod 2^32); epoch = number of this call, starting at 1.
+ *   counter, counter_target  not used any more (the CTAs count themselves in on a word of the
+ *                         workspace); kept so that callers need not change.  epoch = number of
+ *                         this call, starting at 1.
  * Use two output buffers alternately (by epoch parity): a rank may be one call ahead of a peer
  * that still reads the previous result.  A wait that runs out sets B2KV_DEV_WAIT_TIMEOUT in
  * dev_status and returns; nothing spins for ever.

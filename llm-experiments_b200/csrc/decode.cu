@@ -48,15 +48,15 @@ struct StageMeta {
     int bh;              // sequence * H + head
 };
 
-// Optional epilogue of the merge kernel: instead of writing its row to a local output, every
-// CTA stores it straight into the output buffers of all ranks (peer memory over NVLink) at this
-// rank's head offset, and the last CTA to finish raises this rank's flag on every rank.
+// Fused all-gather: instead of writing an output row to a local buffer, the split kernel's merging warps
+// store it straight into the output buffers of all ranks (peer memory over NVLink) at this rank's head
+// offset, and the last CTA of the launch to finish raises this rank's flag on every rank.
 struct GatherInfo {
     void* const* peer_out;        // device array [world]: each rank's [B, h_total * D] output buffer (null = off)
     uint32_t* const* peer_flags;  // device array [world]: each rank's flag words, one per source rank
     const uint32_t* my_flags;     // this rank's own flag words (what the wait kernel watches)
-    unsigned int* counter;        // local: merge CTAs finished so far, never reset
-    unsigned int counter_target;  // value of the counter when this call's last CTA has finished
+    unsigned int* counter;        // (not used any more: the CTAs count themselves in on a word of the workspace)
+    unsigned int counter_target;
     int rank, world, h_total;
     uint32_t epoch;               // value written to the flags by this call
 };
@@ -84,7 +84,10 @@ struct DecodeParams {
     float* partial_out;  // non-null: the merge kernel writes (unnormalised row, max, sum) instead of the output
     // Merge inside the split kernel (plain decode only): the CTA that finishes the last piece of a (sequence, head)
     // merges the pair's partials and writes the output row, so that no second launch is needed.
-    void* fused_out;                 // output [B, H*D] of the storage type; null = the merge kernel writes it
+    int merge_inside;                // 1: the split kernel writes the output rows itself; 0: the merge kernel does
+    void* fused_out;                 // output [B, H*D] of the storage type for the merge inside, unless the rows go
+                                     // to the ranks' buffers (gather.peer_out)
+    unsigned long long* ws_done;     // CTAs of the launch that have finished, tagged like ws_counter (fused gather)
     unsigned long long* ws_tickets;  // [B*H]: (low 40 bits of the call number << 24) | pieces of the pair finished in that call
     unsigned long long call_id;      // unique per launch call, 48 bits, never 0: tickets left by other calls never count
                                      // (a finished pair's ticket goes back to 0, for launches replayed from a graph)
@@ -488,6 +491,19 @@ __device__ __forceinline__ void decode_producer(const DecodeParams& p, const CUt
         (void)mbar_wait(&full[f % STAGES], static_cast<uint32_t>((f / STAGES) & 1));
 }
 
+// Where a finished output element goes when the split kernel writes the rows itself: the local output, or -
+// fused all-gather - the buffer of every rank at this rank's heads (plain peer stores over NVLink).
+template <typename T, int D>
+__device__ __forceinline__ void store_output(const DecodeParams& p, int bh, int d, T val) {
+    if (p.gather.peer_out == nullptr) {
+        static_cast<T*>(p.fused_out)[static_cast<size_t>(bh) * D + d] = val;
+        return;
+    }
+    const int b = bh / p.H, h = bh - b * p.H;
+    const size_t col = (static_cast<size_t>(b) * p.gather.h_total + static_cast<size_t>(p.gather.rank) * p.H + h) * D + d;
+    for (int w = 0; w < p.gather.world; ++w) static_cast<T*>(p.gather.peer_out[w])[col] = val;
+}
+
 // --------------------------------------------------------------------------------------
 // consumer warps
 // --------------------------------------------------------------------------------------
@@ -515,14 +531,14 @@ __device__ __forceinline__ void decode_consumer(const DecodeParams& p, uint8_t* 
     }
 
     // Sequences without tokens own no work item: their output rows are zeros, written here (the CTAs share them out).
-    if (p.fused_out != nullptr) {
-        T* out = static_cast<T*>(p.fused_out);
+    if (p.merge_inside) {
         const int row_elems = p.H * D;
         for (int b = blockIdx.x; b < p.B; b += gridDim.x) {
             if (seq_len_of(p, b) != 0) continue;
             for (int i = warp * 32 + lane; i < row_elems; i += NCW * 32)
-                out[static_cast<size_t>(b) * row_elems + i] = Elt<T>::from_float(0.f);
+                store_output<T, D>(p, b * p.H + i / D, i % D, Elt<T>::from_float(0.f));
         }
+        if (p.gather.peer_out != nullptr) __threadfence_system();  // (before this CTA counts itself in)
     }
 
     int stage = 0;
@@ -698,7 +714,25 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
             return;
         }
         const StageMeta mt = hand_meta[buf];
-        if (mt.flags & kFlagDone) return;
+        if (mt.flags & kFlagDone) {
+            // Fused all-gather: this CTA's rows are on their way to the ranks.  Fence them, count the CTA in; the
+            // last CTA of the launch raises this rank's flag on every rank (and leaves the count at zero for a
+            // launch replayed from a graph).
+            if (p.merge_inside && p.gather.peer_out != nullptr) {
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0 && tagged_count(p.ws_done, p.call_id) == static_cast<long long>(gridDim.x)) {
+                    __threadfence_system();
+                    for (int w = 0; w < p.gather.world; ++w) {
+                        volatile uint32_t* flag = p.gather.peer_flags[w] + p.gather.rank;
+                        *flag = p.gather.epoch;
+                    }
+                    __threadfence_system();
+                    *p.ws_done = 0ull;
+                }
+            }
+            return;
+        }
         const float* mr = merge + buf * Cfg::kMergeFloats;
         float m_all = -INFINITY;
 #pragma unroll
@@ -724,14 +758,13 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
         __syncwarp();
         if (lane == 0) mbar_arrive(&hand_empty[buf]);  // the buffer and its description may be written again
 
-        if (p.fused_out != nullptr && (mt.flags & kFlagWhole)) {
+        if (p.merge_inside && (mt.flags & kFlagWhole)) {
             // the whole (sequence, head) was this one item: its row is final
             // (divided, not multiplied by a reciprocal: bit for bit what the merge kernel gives)
-            T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(mt.bh) * D;
 #pragma unroll
             for (int i = 0; i < CPM; ++i) {
                 const int d = lane + 32 * i;
-                if (d < D) orow[d] = Elt<T>::from_float(o[i] / l_all);
+                if (d < D) store_output<T, D>(p, mt.bh, d, Elt<T>::from_float(o[i] / l_all));
             }
             continue;
         }
@@ -744,7 +777,7 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
             p.ws_ml[static_cast<size_t>(mt.slot) * 2] = m_all;
             p.ws_ml[static_cast<size_t>(mt.slot) * 2 + 1] = l_all;
         }
-        if (p.fused_out == nullptr) continue;  // a merge kernel follows this launch
+        if (!p.merge_inside) continue;  // a merge kernel follows this launch
         // One piece of several.  Publish it (fence), take a ticket for the pair: the CTA that takes the pair's last
         // ticket finds every piece in the workspace and merges them.  Nobody waits for another CTA.
         __threadfence();
@@ -822,11 +855,10 @@ __device__ __forceinline__ void decode_merger(const DecodeParams& p, uint64_t* h
                 add_pieces();
             }
         }
-        T* orow = static_cast<T*>(p.fused_out) + static_cast<size_t>(bh) * D;
 #pragma unroll
         for (int i = 0; i < CPM; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) orow[d] = Elt<T>::from_float(og[i] / l_g);
+            if (d < D) store_output<T, D>(p, bh, d, Elt<T>::from_float(og[i] / l_g));
         }
         // Every piece of the pair has come in, so nobody touches its ticket again in this launch: leave
         // it at zero.  A launch replayed from a CUDA graph carries the number it was captured with, and
@@ -954,30 +986,7 @@ __global__ void __launch_bounds__(D < 32 ? 32 : D) decode_combine_kernel(const D
         }
         return;
     }
-    const T val = Elt<T>::from_float(n > 0 ? o / l_all : 0.f);
-    if (p.gather.peer_out == nullptr) {
-        if (d < D) out[static_cast<size_t>(bh) * D + d] = val;
-        return;
-    }
-    // fused all-gather: the row goes to every rank's buffer, at this rank's heads
-    if (d < D) {
-        const size_t col = (static_cast<size_t>(b) * p.gather.h_total + static_cast<size_t>(p.gather.rank) * p.H + h) * D + d;
-        for (int w = 0; w < p.gather.world; ++w) static_cast<T*>(p.gather.peer_out[w])[col] = val;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int ticket = atomicAdd(p.gather.counter, 1u);
-        if (ticket + 1u == p.gather.counter_target) {
-            // every merge CTA of this call has stored and fenced its rows: publish
-            __threadfence_system();
-            for (int w = 0; w < p.gather.world; ++w) {
-                volatile uint32_t* flag = p.gather.peer_flags[w] + p.gather.rank;
-                *flag = p.gather.epoch;
-            }
-            __threadfence_system();
-        }
-    }
+    if (d < D) out[static_cast<size_t>(bh) * D + d] = Elt<T>::from_float(n > 0 ? o / l_all : 0.f);
 }
 
 // Waits (bounded) until every rank's flag has reached `epoch`: lane w watches rank w.  The flags
@@ -1073,15 +1082,17 @@ static int launch_decode(DecodeParams p, void* out, void* workspace, size_t work
     const size_t acc_bytes = align_up(slots * D * sizeof(float), 256);
     const size_t ml_bytes = align_up(slots * 2 * sizeof(float), 8);
     const size_t ticket_bytes = static_cast<size_t>(p.B) * p.H * sizeof(unsigned long long);
-    const size_t need = acc_bytes + ml_bytes + ticket_bytes + sizeof(unsigned long long);
+    const size_t need = acc_bytes + ml_bytes + ticket_bytes + 2 * sizeof(unsigned long long);
     if (workspace == nullptr || workspace_bytes < need) return B2KV_ERR_WORKSPACE;
     p.ws_acc = static_cast<float*>(workspace);
     p.ws_ml = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
     p.ws_tickets = reinterpret_cast<unsigned long long*>(static_cast<char*>(workspace) + acc_bytes + ml_bytes);
     p.ws_counter = p.ws_tickets + static_cast<size_t>(p.B) * p.H;
-    // The plain decode merges inside the split kernel; the forms whose merge has more to do (peer stores of the
-    // fused all-gather, unnormalised partials of the sequence split) keep the merge kernel.
-    const bool fused_merge = p.gather.peer_out == nullptr && p.partial_out == nullptr && !tune_get("decode_merge_kernel");
+    p.ws_done = p.ws_counter + 1;
+    // The decode merges inside the split kernel, with the fused all-gather's peer stores too; the sequence split,
+    // whose merge leaves unnormalised partials, keeps the merge kernel.
+    const bool fused_merge = p.partial_out == nullptr && (p.gather.peer_out != nullptr || !tune_get("decode_merge_kernel"));
+    p.merge_inside = fused_merge ? 1 : 0;
     p.fused_out = fused_merge ? out : nullptr;
     p.call_id = next_call_id();
 
@@ -1229,7 +1240,7 @@ size_t b2kv_decode_workspace_bytes(int B, int H, int D, int T_upper, int dtype) 
     (void)T_upper;
     const size_t slots = partial_slots(device_sm_count() * kMaxCtasPerSm, B, H);
     return align_up(slots * D * sizeof(float), 256) + align_up(slots * 2 * sizeof(float), 8) +
-           static_cast<size_t>(B) * H * sizeof(unsigned long long) + sizeof(unsigned long long) + 256;
+           static_cast<size_t>(B) * H * sizeof(unsigned long long) + 2 * sizeof(unsigned long long) + 256;
 }
 
 int b2kv_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* seq_lens, int len,
@@ -1309,7 +1320,7 @@ extern "C" int b2kv_decode_allgather(const void* q, const void* k_cache, const v
                                      size_t workspace_bytes, void* const* peer_out, uint32_t* const* peer_flags,
                                      const uint32_t* my_flags, uint32_t* counter, uint32_t counter_target, int rank,
                                      int world, int H_total, uint32_t epoch, int32_t* dev_status, void* stream) {
-    if (!peer_out || !peer_flags || !counter) return B2KV_ERR_BAD_ARG;
+    if (!peer_out || !peer_flags) return B2KV_ERR_BAD_ARG;
     if (world < 1 || world > 32 || rank < 0 || rank >= world || H_total != H_local * world) return B2KV_ERR_BAD_ARG;
     GatherInfo g{peer_out, peer_flags, my_flags, counter, counter_target, rank, world, H_total, epoch};
     return decode_entry(q, k_cache, v_cache, nullptr, seq_lens, len, len_bias, nullptr, 0, 0, 0, B, H_local, D, T_upper,

@@ -88,12 +88,13 @@ def head_split_decode(local_attention: Callable[[torch.Tensor], torch.Tensor], q
 
 
 class FusedHeadGather:
-    """Head-split decode whose all-gather is fused into the merge kernel (``b2kv_decode_allgather``).
+    """Head-split decode whose all-gather is fused into the decode kernel (``b2kv_decode_allgather``).
 
-    Every rank owns ``H/W`` heads.  The merge kernel of each rank stores its output rows directly
-    into the ``[B, H*D]`` result buffers of all ranks over NVLink (symmetric memory obtained from
-    ``torch.distributed._symmetric_memory``), raises a flag on every rank, and a bounded wait on
-    the rank's own flags ends the call: no NCCL collective, no extra pass over the data.  Two
+    Every rank owns ``H/W`` heads.  The decode kernel of each rank stores its output rows, as they
+    are finished, directly into the ``[B, H*D]`` result buffers of all ranks over NVLink (symmetric
+    memory obtained from ``torch.distributed._symmetric_memory``); its last CTA raises a flag on every
+    rank, and a bounded wait on the rank's own flags ends the call: no NCCL collective, no second
+    kernel, no extra pass over the data.  Two
     result buffers are used alternately, so a rank that runs one step ahead never overwrites a
     result that a slower peer is still reading.
     """
@@ -138,9 +139,7 @@ class FusedHeadGather:
     def _setup_tables(self, device, out_ptrs, flag_ptrs):
         self._out_tables = [torch.tensor(ptrs, dtype=torch.int64, device=device) for ptrs in out_ptrs]
         self._flag_table = torch.tensor(flag_ptrs, dtype=torch.int64, device=device)
-        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.epoch = 0
-        self.counter_target = 0
 
     def decode(self, ctx, cache, layer_idx: int, q_local, wait: bool = True) -> torch.Tensor:
         """Attention of this rank's heads over its cache slice; returns the ``[B, H*D]`` result of
@@ -156,7 +155,6 @@ class FusedHeadGather:
         if cache.current_len == 0:
             raise ValueError("Cache is empty: current_len=0")
         self.epoch = (self.epoch + 1) & 0xFFFFFFFF
-        self.counter_target = (self.counter_target + self.B * self.H_local) & 0xFFFFFFFF
         buf = self.epoch & 1
         ws = decode_workspace(cache)
         stream = batch_op_begin(ctx)
@@ -167,7 +165,7 @@ class FusedHeadGather:
             None if cache.seq_lens is None else cache.seq_lens.data_ptr(), cache.current_len, 0, self.B, self.H_local,
             self.D, min(cache.current_len, cache.max_seq_len), s0, st, sh, dtype_code(cache.dtype), ws.data_ptr(),
             ws.numel(), self._out_tables[buf].data_ptr(), self._flag_table.data_ptr(),
-            self.flags.data_ptr() if wait else None, self.counter.data_ptr(), self.counter_target, self.rank,
+            self.flags.data_ptr() if wait else None, None, 0, self.rank,
             self.world, self.H_total, self.epoch, dev_status_ptr(ctx), stream)
         _native.check(rc)
         return self.out[buf]
