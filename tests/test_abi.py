@@ -88,6 +88,9 @@ def test_argument_checks_return_before_any_launch(pkg):
     assert lib.b2kv_matmul(A, A, None, None, A, 256, 100, 128, 0, 1, None, None) == -3
     assert lib.b2kv_matmul(A, A, None, A + 2, A, 256, 128, 128, 0, 1, None, None) == -2
     assert lib.b2kv_matmul(A, A, None, None, A, 256, 128, 128, 2, 1, None, None) == -1
+    # length advance: no lengths, no sequences
+    assert lib.b2kv_advance_lengths(None, 4, 1, None) == -1
+    assert lib.b2kv_advance_lengths(A, 0, 1, None) == -1
 
 
 def test_workspace_size_grows_with_the_problem(pkg):

@@ -484,3 +484,20 @@ def test_decode_with_chunks_on_demand_replayed_from_a_cuda_graph(pkg, ctx):
     finally:
         pkg._native.tune("decode_dynamic_chunks", 0)
     assert int(ctx.dev_status.item()) == 0
+
+
+def test_advance_lengths_in_stream_order(pkg, ctx):
+    """``b2kv_advance_lengths`` adds to the device-side lengths of a ragged cache, ordered with the kernels of its
+    stream: an append that does not advance, the advance, then a decode over the lengths it left."""
+    gpu = pkg.gpu
+    B, H, D, T, dtype = 70, 2, 64, 40, torch.bfloat16
+    E = H * D
+    cache = gpu.kv_cache_create(ctx, gpu.KVCacheConfig(batch_size=B, max_seq_len=T, n_layers=1, n_heads=H, head_dim=D,
+                                                       dtype=dtype, layout="bhtd", ragged=True))
+    lens = [int(x) for x in np.random.default_rng(3).integers(0, T - 3, size=B)]
+    gpu.kv_cache_set_lengths(cache, lens)
+    stream = torch.cuda.current_stream().cuda_stream
+    for delta in (1, 2):
+        pkg._native.check(pkg._native.lib.b2kv_advance_lengths(cache.seq_lens.data_ptr(), B, delta, stream))
+    torch.cuda.synchronize()
+    assert cache.seq_lens.cpu().tolist() == [n + 3 for n in lens]
