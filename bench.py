@@ -101,9 +101,9 @@ SLACK = 1024  # rows of head-room above the longest sequence for the appended to
 # the units a full launch processes.  They describe the DEFAULT kernel variants only and have to be captured again
 # (small case, one kernel, --clock-control none) whenever a kernel or its launch order changes; a run with any
 # --tune knob reports no traffic.
-#   decode_split_kernel<bf16, 128, 64, 3, 8>: 411.7 MB for 24908 tokens x 32 heads of `--workload decode_small`
+#   decode_split_kernel<bf16, 128, 64, 3, 8>: 412.6 MB for 24908 tokens x 32 heads of `--workload decode_small`
 #   (profiles/decode_split_kernel_decode_small.md); the algorithmic figure is 512 B per attended (token, head).
-DRAM_BYTES_PER_TOKEN_HEAD = 516.6
+DRAM_BYTES_PER_TOKEN_HEAD = 517.7
 #   prefill_tc_kernel<128> with launch groups: 212.7 MB read + 155.1 MB written for the 2 sequences of
 #   `--workload prefill_small` (profiles/prefill_tc_kernel_prefill_small.md); algorithmic: 6 x 33.5 MB per sequence.
 PREFILL_DRAM_BYTES_PER_SEQUENCE = int((212.7e6 + 155.1e6) / 2)
